@@ -1,0 +1,150 @@
+"""Host-side mirror of the reference's operator interface.
+
+``flash_attention_v2_cutlass(q, k, v, is_causal=False, softmax_scale=1)`` has the
+name, positional order, defaults and return type (a one-element list) of the
+reference extension's only export (include/attention_api.h:10-11,
+csrc/attention_api.cpp:6-10, csrc/flash_attention.cu:639-668).  torch supplies
+device memory and the current stream; the work is done by libfa8_b200.so through
+its C ABI.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+
+from . import _lib
+
+_status_words = {}
+
+
+def _check_input(x: torch.Tensor, name: str) -> None:
+    # CHECK_INPUT of include/attention_api.cuh:12-18 (TORCH_CHECK -> RuntimeError)
+    if not x.device.type == "cuda":
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not x.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The int32 device word kernels on `device` report an expired wait into."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status_words:
+        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _status_words[idx]
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronises the current stream of `device` and raises RuntimeError if a kernel
+    launched through this module reported an expired wait (or the stream is in error).
+    Stands where the reference has cudaDeviceSynchronize + CUDA_ERROR_CHECK
+    (csrc/flash_attention.cu:663-665), but raises instead of exiting the process."""
+    lib = _lib.load()
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    word = status_word(device)
+    code = ctypes.c_int32(0)
+    with torch.cuda.device(word.device):
+        stream = torch.cuda.current_stream(word.device).cuda_stream
+        rc = lib.fa8_check_status(word.data_ptr(), stream, ctypes.byref(code))
+    if rc != _lib.FA8_OK:
+        word.zero_()
+        raise RuntimeError(_lib.error_message(rc) + f" (device code 0x{code.value:x})")
+
+
+def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                               is_causal: bool = False, softmax_scale: float = 1.0, *,
+                               v_layout: str = "transposed", o_scale: float = 1.0,
+                               out: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
+    """FP8 attention forward.
+
+    q, k: float8_e4m3fn [batch, heads, seqlen, head_dim], CUDA, contiguous.
+    v:    float8_e4m3fn, transposed [batch, heads, head_dim, seqlen] as the reference
+          requires (test.py:71), or [batch, heads, seqlen, head_dim] with
+          v_layout="natural".
+    Returns [O] with O fp16 [batch, heads, seqlen, head_dim] (the reference returns
+    e4m3, csrc/flash_attention.cu:656).  The kernel is enqueued on the current
+    stream; nothing synchronises (the reference blocks, :663-665) - call
+    check_status() to synchronise and surface device-side errors.
+    """
+    lib = _lib.load()
+    _check_input(q, "q")
+    _check_input(k, "k")
+    _check_input(v, "v")
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if t.dtype != torch.float8_e4m3fn:
+            raise RuntimeError(f"{name} must be float8_e4m3fn, got {t.dtype}")
+        if t.dim() != 4:
+            raise RuntimeError(f"{name} must have 4 dimensions [batch, heads, seqlen, head_dim]")
+        if t.device != q.device:
+            raise RuntimeError("q, k and v must be on the same device")
+    B, H, S, D = q.shape
+    if tuple(k.shape) != (B, H, S, D):
+        raise RuntimeError(f"k must have the shape of q {tuple(q.shape)}, got {tuple(k.shape)}")
+    if v_layout == "transposed":
+        want_v, layout = (B, H, D, S), _lib.FA8_V_TRANSPOSED
+    elif v_layout == "natural":
+        want_v, layout = (B, H, S, D), _lib.FA8_V_NATURAL
+    else:
+        raise RuntimeError("v_layout must be 'transposed' or 'natural'")
+    if tuple(v.shape) != want_v:
+        raise RuntimeError(f"v must be {want_v} for v_layout='{v_layout}', got {tuple(v.shape)}")
+    if out is None:
+        out = torch.empty((B, H, S, D), dtype=torch.float16, device=q.device)
+    else:
+        _check_input(out, "out")
+        if out.dtype != torch.float16 or tuple(out.shape) != (B, H, S, D) or out.device != q.device:
+            raise RuntimeError("out must be a float16 CUDA tensor shaped like q")
+    p = _lib.Fa8FwdParams(
+        q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=out.data_ptr(),
+        batch=B, heads=H, seqlen=S, head_dim=D, softmax_scale=float(softmax_scale),
+        is_causal=int(bool(is_causal)), v_layout=layout, o_scale=float(o_scale),
+        status_word=status_word(q.device).data_ptr())
+    with torch.cuda.device(q.device):
+        rc = lib.fa8_fwd(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
+    if rc != _lib.FA8_OK:
+        raise RuntimeError(_lib.error_message(rc))
+    return [out]
+
+
+class HostRunner:
+    """End-to-end call with HOST tensors: pinned host -> device copies, the kernel and
+    the device -> host copy of O all run on one stream; the call returns after O has
+    landed in (pinned) host memory.  Device and pinned buffers are allocated once per
+    shape and reused."""
+
+    def __init__(self, device: Optional[torch.device] = None):
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self._key = None
+
+    def _ensure(self, q: torch.Tensor, v: torch.Tensor):
+        key = (tuple(q.shape), tuple(v.shape))
+        if key == self._key:
+            return
+        B, H, S, D = q.shape
+        dev = self.device
+        self.dq = torch.empty(q.shape, dtype=torch.float8_e4m3fn, device=dev)
+        self.dk = torch.empty(q.shape, dtype=torch.float8_e4m3fn, device=dev)
+        self.dv = torch.empty(v.shape, dtype=torch.float8_e4m3fn, device=dev)
+        self.do = torch.empty((B, H, S, D), dtype=torch.float16, device=dev)
+        self.ho = torch.empty((B, H, S, D), dtype=torch.float16, pin_memory=True)
+        self._key = key
+
+    def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = False,
+                 softmax_scale: float = 1.0, **kw) -> List[torch.Tensor]:
+        for name, t in (("q", q), ("k", k), ("v", v)):
+            if t.device.type != "cpu":
+                raise RuntimeError(f"{name} must be a host tensor")
+        self._ensure(q, v)
+        self.dq.copy_(q, non_blocking=True)
+        self.dk.copy_(k, non_blocking=True)
+        self.dv.copy_(v, non_blocking=True)
+        flash_attention_v2_cutlass(self.dq, self.dk, self.dv, is_causal, softmax_scale, out=self.do, **kw)
+        self.ho.copy_(self.do, non_blocking=True)
+        check_status(self.device)     # synchronises the stream
+        return [self.ho]
+
+    def bytes_per_call(self, q: torch.Tensor, v: torch.Tensor):
+        h2d = 2 * q.numel() + v.numel()
+        d2h = 2 * q.numel()
+        return h2d, d2h

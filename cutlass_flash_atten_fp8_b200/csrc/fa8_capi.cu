@@ -1,0 +1,153 @@
+// C-ABI layer of libfa8_b200.so: argument validation, TMA descriptor
+// construction and kernel launch.  Declared in include/fa8_b200.h.
+//
+// Stands where the reference has flash_attention_v2_cutlass
+// (csrc/flash_attention.cu:639-668), set_params_fprop (:277-318) and the
+// dispatch chain run_flash_attn_cutlass / run_flash_fwd_ / run_flash_fwd
+// (:586-637).  No torch types, no exceptions, no exit().
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "fa8_b200.h"
+#include "fa8_kernel.h"
+
+namespace {
+
+thread_local char g_detail[320] = "";
+
+void set_detail(const char* what, const char* msg) {
+  std::snprintf(g_detail, sizeof(g_detail), "%s: %s", what, msg ? msg : "?");
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled is fetched through the runtime so that the library
+// carries no link-time dependency on libcuda.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 3-D byte tensor {inner, mid, outer} with a {box_inner, box_mid, 1} tile.
+bool make_map_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t mid, uint64_t outer,
+                 uint32_t box_inner, uint32_t box_mid, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) {
+    set_detail("cudaGetDriverEntryPoint", "cuTensorMapEncodeTiled not available");
+    return false;
+  }
+  cuuint64_t dims[3] = {inner, mid, outer};
+  cuuint64_t strides[2] = {inner, inner * mid};   // bytes, for dims 1 and 2
+  cuuint32_t box[3] = {box_inner, box_mid, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
+    set_detail("cuTensorMapEncodeTiled", buf);
+    return false;
+  }
+  return true;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+int fa8_version(void) { return 100; }
+
+const char* fa8_error_string(int code) {
+  switch (code) {
+    case FA8_OK: return "ok";
+    case FA8_ERR_BAD_ARG: return "bad argument (null or misaligned pointer, non-positive size or scale)";
+    case FA8_ERR_UNSUPPORTED: return "unsupported shape or layout (head_dim must be 64 or 128, seqlen a multiple of 16)";
+    case FA8_ERR_CUDA: return "CUDA call failed";
+    case FA8_ERR_DEVICE_TIMEOUT: return "a bounded wait inside the kernel expired";
+    default: return "unknown fa8 status";
+  }
+}
+
+const char* fa8_last_error_detail(void) { return g_detail; }
+
+int fa8_supported(int32_t seqlen, int32_t head_dim, int32_t v_layout) {
+  if (head_dim != 64 && head_dim != 128) return FA8_ERR_UNSUPPORTED;
+  if (seqlen <= 0 || (seqlen % 16) != 0) return FA8_ERR_UNSUPPORTED;
+  if (v_layout != FA8_V_TRANSPOSED) return FA8_ERR_UNSUPPORTED;
+  return FA8_OK;
+}
+
+int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
+  g_detail[0] = '\0';
+  if (!p || !p->q || !p->k || !p->v || !p->o) return FA8_ERR_BAD_ARG;
+  if (p->batch <= 0 || p->heads <= 0 || p->seqlen <= 0 || p->head_dim <= 0) return FA8_ERR_BAD_ARG;
+  if (!(p->softmax_scale > 0.f) || !std::isfinite(p->softmax_scale)) return FA8_ERR_BAD_ARG;
+  if (!std::isfinite(p->o_scale)) return FA8_ERR_BAD_ARG;
+  if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->o)) return FA8_ERR_BAD_ARG;
+  if (p->status_word && (reinterpret_cast<uintptr_t>(p->status_word) & 3u)) return FA8_ERR_BAD_ARG;
+  if (p->v_layout != FA8_V_TRANSPOSED && p->v_layout != FA8_V_NATURAL) return FA8_ERR_BAD_ARG;
+  int sup = fa8_supported(p->seqlen, p->head_dim, p->v_layout);
+  if (sup != FA8_OK) return sup;
+  const int64_t bh = static_cast<int64_t>(p->batch) * p->heads;
+  if (bh > 65535) return FA8_ERR_UNSUPPORTED;   // grid.y
+
+  const uint64_t S = static_cast<uint64_t>(p->seqlen), D = static_cast<uint64_t>(p->head_dim);
+  const CUtensorMapSwizzle sw_qk = (p->head_dim == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUtensorMap tq, tk, tv;
+  if (!make_map_3d(&tq, p->q, D, S, bh, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
+  if (!make_map_3d(&tk, p->k, D, S, bh, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
+  // V^T: [bh, D, S]; a tile is D rows of 128 consecutive key positions.
+  if (!make_map_3d(&tv, p->v, S, D, bh, 128, static_cast<uint32_t>(D), CU_TENSOR_MAP_SWIZZLE_128B)) return FA8_ERR_CUDA;
+
+  fa8::KernelArgs args;
+  args.o = static_cast<__half*>(p->o);
+  args.seqlen = p->seqlen;
+  args.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  args.o_scale = p->o_scale;
+  args.status = p->status_word;
+  args.timeout_ns = 2000000000ull;
+  const int n_pairs = (p->seqlen + 255) / 256;
+  cudaError_t e = fa8::launch_fwd(p->head_dim, p->is_causal != 0, tq, tk, tv, args, n_pairs,
+                                  static_cast<int>(bh), static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) {
+    set_detail("kernel launch", cudaGetErrorString(e));
+    return FA8_ERR_CUDA;
+  }
+  return FA8_OK;
+}
+
+int fa8_check_status(const int32_t* status_word, void* cuda_stream, int32_t* code_out) {
+  g_detail[0] = '\0';
+  if (!status_word) return FA8_ERR_BAD_ARG;
+  int32_t host = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  cudaError_t e = cudaMemcpyAsync(&host, status_word, sizeof(host), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) {
+    set_detail("status read-back", cudaGetErrorString(e));
+    return FA8_ERR_CUDA;
+  }
+  if (code_out) *code_out = host;
+  return host == 0 ? FA8_OK : FA8_ERR_DEVICE_TIMEOUT;
+}
+
+}  // extern "C"

@@ -1,0 +1,27 @@
+// Internal interface between the C-ABI layer (fa8_capi.cu) and the sm_100a
+// kernel (fa8_fwd_sm100.cu).  Not installed; callers use include/fa8_b200.h.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+namespace fa8 {
+
+// By-value kernel arguments.  Plays the role of the reference's
+// Flash_fwd_params (csrc/flash.h:6-61) minus its dead fields; tensor addresses
+// and strides travel in the three TMA descriptors instead.
+struct KernelArgs {
+  __half* o;                      // [batch*heads, seqlen, head_dim] fp16
+  int seqlen;                     // queries == keys
+  float scale_log2;               // softmax_scale * log2(e)
+  float o_scale;                  // multiplies O/l (1 = reference behaviour)
+  int* status;                    // optional device word; non-zero after a bounded wait expired
+  unsigned long long timeout_ns;  // bound of every mbarrier wait
+};
+
+// Launches the forward kernel for head_dim in {64,128}; grid = (n_pairs, bh).
+cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
+                       const CUtensorMap& tv, const KernelArgs& args, int n_pairs, int bh,
+                       cudaStream_t stream);
+
+}  // namespace fa8

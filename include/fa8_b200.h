@@ -1,0 +1,94 @@
+/*
+ * fa8_b200.h - C ABI of the B200 (sm_100a) FP8 flash-attention forward.
+ *
+ * This is the boundary a foreign-language binding loads (libfa8_b200.so):
+ * plain pointers and sizes, a CUDA stream handle passed as void*, an int
+ * status as the return value.  No C++ or torch types cross it.
+ *
+ * It replaces the host entry of the reference extension,
+ *   std::vector<torch::Tensor> flash_attention_v2_cutlass(q, k, v, is_causal,
+ *   softmax_scale)            (include/attention_api.h:10-11,
+ *                              csrc/flash_attention.cu:639-668),
+ * i.e. set_params_fprop (csrc/flash_attention.cu:277-318), the dtype/head_dim/
+ * causal dispatch (:618-637, csrc/static_switch.h) and run_flash_fwd (:586-610).
+ * Differences, all deliberate:
+ *   - the output is fp16 (the reference stores e4m3, :656 and :556-557);
+ *   - the kernel is launched on the caller's stream and the call does not
+ *     synchronise the device (the reference uses stream 0 and calls
+ *     cudaDeviceSynchronize, :608-609 and :663-665);
+ *   - errors come back as codes (the reference prints and exit()s,
+ *     include/attention_api.cuh:20-29);
+ *   - arguments are validated (the reference checks only device/contiguity,
+ *     include/attention_api.cuh:12-18).
+ */
+#ifndef FA8_B200_H_
+#define FA8_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA8_OK 0
+#define FA8_ERR_BAD_ARG (-1)        /* null pointer, non-positive size, misaligned pointer, bad scale */
+#define FA8_ERR_UNSUPPORTED (-2)    /* shape or layout outside what the kernel implements */
+#define FA8_ERR_CUDA (-3)           /* a CUDA runtime/driver call failed; see fa8_last_error_detail */
+#define FA8_ERR_DEVICE_TIMEOUT (-4) /* a bounded wait inside the kernel expired (status word != 0) */
+
+/* Layout of V.  The reference requires the caller to pass V transposed,
+ * [batch, heads, head_dim, seqlen] (test.py:71, csrc/flash_attention.cu:376-379). */
+#define FA8_V_TRANSPOSED 0 /* [batch, heads, head_dim, seqlen], seqlen contiguous (reference layout) */
+#define FA8_V_NATURAL 1    /* [batch, heads, seqlen, head_dim], head_dim contiguous */
+
+/* Arguments of one forward call; mirrors the live fields of the reference's
+ * Flash_fwd_params (csrc/flash.h:6-61).  All tensors are contiguous device
+ * memory, 16-byte aligned. */
+typedef struct fa8_fwd_params {
+  const void* q;   /* e4m3 [batch, heads, seqlen, head_dim] */
+  const void* k;   /* e4m3 [batch, heads, seqlen, head_dim] */
+  const void* v;   /* e4m3, layout given by v_layout */
+  void* o;         /* fp16 [batch, heads, seqlen, head_dim], written by the call */
+  int32_t batch;
+  int32_t heads;
+  int32_t seqlen;    /* queries and keys alike (the reference has no other case); multiple of 16 */
+  int32_t head_dim;  /* 64 or 128 */
+  float softmax_scale; /* > 0; P = exp(softmax_scale * (S - rowmax)) */
+  int32_t is_causal;   /* 0/1; mask is lower-triangular including the diagonal (test.py:25-33) */
+  int32_t v_layout;    /* FA8_V_TRANSPOSED or FA8_V_NATURAL */
+  float o_scale;       /* O is multiplied by this; 1.0f reproduces the reference; a caller with
+                          per-tensor scaled inputs folds V's descale here and Q's and K's into
+                          softmax_scale */
+  int32_t* status_word; /* optional device int32, zero before the call; the kernel stores a
+                           non-zero code there if one of its bounded waits runs out */
+} fa8_fwd_params;
+
+/* Enqueues the forward on `cuda_stream` (a cudaStream_t; NULL = default stream)
+ * of the current device.  Returns FA8_OK when the launch was accepted.  Replaces
+ * flash_attention_v2_cutlass (csrc/flash_attention.cu:639-668). */
+int fa8_fwd(const fa8_fwd_params* params, void* cuda_stream);
+
+/* Reads a status word back after synchronising `cuda_stream`: FA8_OK,
+ * FA8_ERR_DEVICE_TIMEOUT (code copied to *code_out if not NULL) or FA8_ERR_CUDA.
+ * Replaces the reference's cudaDeviceSynchronize + CUDA_ERROR_CHECK
+ * (csrc/flash_attention.cu:663-665). */
+int fa8_check_status(const int32_t* status_word, void* cuda_stream, int32_t* code_out);
+
+/* Says whether fa8_fwd implements this shape: FA8_OK or FA8_ERR_UNSUPPORTED.  Replaces the
+ * head_dim switch of the reference (csrc/static_switch.h:50-77). */
+int fa8_supported(int32_t seqlen, int32_t head_dim, int32_t v_layout);
+
+/* Static text for a return code.  Replaces the message printed by CUDA_ERROR_CHECK
+ * (include/attention_api.cuh:20-29). */
+const char* fa8_error_string(int code);
+
+/* Text of the last CUDA failure seen by the calling thread (empty string if none). */
+const char* fa8_last_error_detail(void);
+
+/* ABI version of this header: major*100 + minor. */
+int fa8_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA8_B200_H_ */
