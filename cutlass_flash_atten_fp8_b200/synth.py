@@ -54,6 +54,9 @@ WORKLOADS: Dict[str, Workload] = {
     "prefill_s1024_d64": Workload("prefill_s1024_d64", 16, 32, 1024, 64, False, seed=1002),
     "mid_s4096_d128": Workload("mid_s4096_d128", 16, 32, 4096, 128, False, outliers=True, seed=1003),
     "mid_s4096_d128_causal": Workload("mid_s4096_d128_causal", 16, 32, 4096, 128, True, outliers=True, seed=1003),
+    # batch-2 cuts of the mid-length shape: small enough for a multi-pass profiler capture, still larger than L2
+    "mid_s4096_d128_b2": Workload("mid_s4096_d128_b2", 2, 32, 4096, 128, False, outliers=True, seed=1003),
+    "mid_s4096_d128_b2_causal": Workload("mid_s4096_d128_b2_causal", 2, 32, 4096, 128, True, outliers=True, seed=1003),
     "long_s16384_d128_causal": Workload("long_s16384_d128_causal", 1, 32, 16384, 128, True, seed=1004),
     "box_s8192_d128_causal": Workload("box_s8192_d128_causal", 64, 32, 8192, 128, True, seed=1005),
 }

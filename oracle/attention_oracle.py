@@ -192,3 +192,17 @@ def error_metrics(out: torch.Tensor, ref: torch.Tensor) -> dict:
         "rel_l2": float(diff.norm() / max(ref.norm(), 1e-30)),
         "max_ref": float(ref.abs().max()),
     }
+
+
+def attention_fp32_rows(q8, k8, v8, rows, causal: bool, softmax_scale: float) -> torch.Tensor:
+    """attention_fp32 for ONE slice and a subset of its query rows: q8,k8,v8 are [S,D]
+    (V not transposed), `rows` a 1-D index tensor.  Returns fp32 [len(rows), D].  Lets a
+    test check a long sequence without the full S x S score matrix."""
+    q = _as_f32(q8)[rows]
+    k = _as_f32(k8)
+    v = _as_f32(v8)
+    p = (q @ k.T) * softmax_scale
+    if causal:
+        cols = torch.arange(k.shape[0]).unsqueeze(0)
+        p = p.masked_fill(cols > rows.unsqueeze(1), float("-inf"))
+    return torch.softmax(p, dim=-1) @ v

@@ -1,0 +1,62 @@
+"""The C-ABI library loads without a GPU and exports what include/fa8_b200.h declares.
+No compute call is made here."""
+import ctypes
+import os
+import re
+
+from cutlass_flash_atten_fp8_b200 import _lib
+from cutlass_flash_atten_fp8_b200.build import LIB_PATH, REPO_DIR, build
+
+
+def _declared_functions():
+    text = open(os.path.join(REPO_DIR, "include", "fa8_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fa8_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_builds_and_loads():
+    build()
+    assert os.path.exists(LIB_PATH)
+    lib = _lib.load()
+    assert lib.fa8_version() == 100
+
+
+def test_every_declared_symbol_is_exported():
+    raw = ctypes.CDLL(LIB_PATH)
+    declared = _declared_functions()
+    assert set(declared) == set(_lib.EXPORTED_SYMBOLS)
+    for name in declared:
+        assert hasattr(raw, name), name
+
+
+def test_error_strings_and_support_query():
+    lib = _lib.load()
+    for code in (0, -1, -2, -3, -4):
+        assert len(lib.fa8_error_string(code)) > 0
+    assert lib.fa8_error_string(-99) == b"unknown fa8 status"
+    assert lib.fa8_supported(4096, 128, _lib.FA8_V_TRANSPOSED) == _lib.FA8_OK
+    assert lib.fa8_supported(128, 64, _lib.FA8_V_TRANSPOSED) == _lib.FA8_OK
+    assert lib.fa8_supported(128, 96, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
+    assert lib.fa8_supported(100, 64, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
+    assert lib.fa8_supported(0, 64, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
+
+
+def test_argument_validation_needs_no_gpu():
+    lib = _lib.load()
+    assert lib.fa8_fwd(None, None) == _lib.FA8_ERR_BAD_ARG
+    p = _lib.Fa8FwdParams()          # all zero: null pointers
+    assert lib.fa8_fwd(ctypes.byref(p), None) == _lib.FA8_ERR_BAD_ARG
+    fake = 0x1000                    # never dereferenced: validation fails first
+    p = _lib.Fa8FwdParams(q=fake, k=fake, v=fake, o=fake, batch=1, heads=1, seqlen=128, head_dim=64,
+                          softmax_scale=0.0, is_causal=0, v_layout=0, o_scale=1.0, status_word=None)
+    assert lib.fa8_fwd(ctypes.byref(p), None) == _lib.FA8_ERR_BAD_ARG          # scale must be > 0
+    p.softmax_scale = 0.125
+    p.q = fake + 8
+    assert lib.fa8_fwd(ctypes.byref(p), None) == _lib.FA8_ERR_BAD_ARG          # 16-byte alignment
+    p.q = fake
+    p.head_dim = 96
+    assert lib.fa8_fwd(ctypes.byref(p), None) == _lib.FA8_ERR_UNSUPPORTED
+    p.head_dim = 64
+    p.v_layout = 7
+    assert lib.fa8_fwd(ctypes.byref(p), None) == _lib.FA8_ERR_BAD_ARG
+    assert lib.fa8_check_status(None, None, None) == _lib.FA8_ERR_BAD_ARG
