@@ -349,7 +349,7 @@ def main():
         if world == 1:
             line["reference_kernel"] = reference_kernel_tflops(w, q4, k4, v4, args.steps)
             if not args.no_cpu_baseline:
-                line["cpu_baseline"] = cpu_attention_tflops(w, 12.0, 64, w.name)
+                line["cpu_baseline"] = cpu_attention_tflops(w, 12.0, w.n_slices, w.name)
                 line["cpu_baseline"].pop("seconds_per_slice", None)
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -195,7 +195,7 @@ def test_box_scale_config_shape():
     def draw(shape):
         t = torch.empty(shape, dtype=F8, device=d)
         for i in range(0, n, 128):
-            t[i:i + 128] = (torch.randn((128,) + shape[1:], generator=g, device=d) * 100.0).to(F8)
+            t[i:i + 128] = (torch.randn((128,) + shape[1:], generator=g, device=d) * 100.0).clamp(-448.0, 448.0).to(F8)
         return t
     q8, k8, vt8 = draw((n, S, D)), draw((n, S, D)), draw((n, D, S))
     scale = w.softmax_scale / 100.0 / 100.0
