@@ -6,26 +6,34 @@
 // csrc/mma_traits_sm89.hpp) and the C->A register shuffle (csrc/reg2reg.h).
 //
 // One CTA owns two 128-row query tiles of one (batch, head) slice and walks the
-// key/value sequence in blocks of 128:
+// key/value sequence; K and V^T arrive as 128-position tiles, the arithmetic runs
+// on 64-position sub-blocks so that each query tile has TWO score buffers in
+// tensor memory and its next S = Q K^T is computed while the softmax of the
+// current sub-block is still running:
 //
 //   warp 9      TMA producer: Q tiles once, then K_j / V_j tiles into a ring of
 //               shared-memory slots, each guarded by a full/empty mbarrier pair.
-//   warp 8      MMA issuer (one elected lane): S_i = Q_i K_j^T and
-//               O_i += P_i V_j as tcgen05.mma kind::f8f6f4 with fp32
-//               accumulators in tensor memory; completion is signalled with
-//               tcgen05.commit on mbarriers.
+//   warp 8      MMA issuer (one elected lane): S_i[sb&1] = Q_i K_sb^T (M128 N64)
+//               and O_i += P_i(sb) V_sb (M128 N=head_dim) as tcgen05.mma
+//               kind::f8f6f4 with fp32 accumulators in tensor memory; completion
+//               is signalled with tcgen05.commit on mbarriers.
 //   warps 0-3   online softmax for query tile 0 (one TMEM lane = one row per
-//   warps 4-7   thread), resp. tile 1: rowmax, exp2 with the scale folded in,
-//               row sum from the fp32 probabilities, fp32 rescale of O in TMEM
-//               when a row maximum grew, P re-quantised to e4m3 and written
-//               back to TMEM over S as the A operand of the second GEMM.
+//   warps 4-7   thread), resp. tile 1: exp2 with the scale folded in, row sum from
+//               the fp32 probabilities, P re-quantised to e4m3 and written back to
+//               TMEM over its own S buffer as the A operand of the second GEMM;
+//               fp32 rescale of O in TMEM when the row maximum has to be raised.
 //
-// While one tile's softmax runs, the tensor core works on the other tile.
-// Numerics follow the reference: P = exp(scale*(S - rowmax)) unnormalised in
-// [0,1], converted to e4m3 round-to-nearest-even/saturating
-// (csrc/flash_attention.cu:163-179,524), the row sum taken from fp32 P
-// (:239-240,:264-271), final O/l with the zero/NaN guard (:542-554).  The output
-// is fp16 (the reference rounds it to e4m3, :556-557).
+// TMEM columns: tile i has S buffers at 128*i and 128*i+64 (64 fp32 columns each;
+// P, 64 e4m3 = 16 columns, overlays the buffer it was computed from) and O_i at
+// 256 + head_dim*i.
+//
+// Numerics follow the reference: P = exp(scale*(S - m)) unnormalised, converted to
+// e4m3 round-to-nearest-even/saturating (csrc/flash_attention.cu:163-179,524), the
+// row sum taken from fp32 P (:239-240,:264-271), final O/l with the zero/NaN guard
+// (:542-554).  Differences: the output is fp16 (the reference rounds it to e4m3,
+// :556-557); m is the exact row maximum after the first sub-block and is then
+// raised only when a sub-block would push P beyond 2^8 (the reference raises it on
+// every block, :233-273), which leaves O/l unchanged up to the rounding of P.
 //
 // Every mbarrier wait is bounded: when a wait runs out, the waiting thread
 // records a code in the caller's status word, raises a CTA-wide abort flag and
@@ -45,8 +53,8 @@ namespace fa8 {
 namespace {
 
 constexpr int kTileM = 128;        // query rows per tile = TMEM lanes
-constexpr int kBlockN = 128;       // key/value rows per block
-constexpr int kSoftmaxWarps = 8;   // 2 tiles x 4 warps
+constexpr int kBlockN = 128;       // key/value positions per TMA tile
+constexpr int kSubN = 64;          // key/value positions per MMA / softmax sub-block
 constexpr int kMmaWarp = 8;
 constexpr int kLoadWarp = 9;
 constexpr int kThreads = 320;
@@ -61,7 +69,7 @@ struct Cfg {
   static constexpr int kQBytes = 2 * kTileBytes;
   static constexpr int kRingBytes = kSlots * kTileBytes;
   static constexpr int kBarOffset = kQBytes + kRingBytes;
-  static constexpr int kNumBars = 2 /*q_full*/ + 2 * kSlots + 2 /*s_full*/ + 2 /*p_full*/ + 1 /*drain*/;
+  static constexpr int kNumBars = 2 /*q_full*/ + 2 * kSlots + 4 /*s_full*/ + 4 /*p_full*/ + 2 /*o_done*/ + 2 /*o_final*/ + 1 /*drain*/;
   static constexpr int kSmemBytes = kBarOffset + kNumBars * 8 + 16 /*tmem ptr, abort*/ + 1024 /*align*/;
   // Q and K rows are D bytes long: one 128-byte swizzle row for D=128, a 64-byte one for D=64.
   static constexpr uint32_t kQKLayout = (D == 128) ? 2u : 4u;   // UMMA SWIZZLE_128B / SWIZZLE_64B
@@ -107,6 +115,112 @@ __device__ __forceinline__ bool wait_bounded(const WaitCtx& w, uint32_t bar, uin
   }
 }
 
+// ------------------------------------------------------------ softmax passes
+// Which of the 16 element pairs of a 32-column chunk take their exponential on the FMA
+// pipe instead of the special-function unit (bit p = pair p).
+#ifndef FA8_POLY_PAIR_MASK
+#define FA8_POLY_PAIR_MASK 0x4925
+#endif
+// P may grow to kLazyLimit (<= 448, the e4m3 maximum, with room for the polynomial
+// path's clamp at 2^8) before the row maximum is raised.
+constexpr float kLazyLimit = 128.f;
+
+#ifdef FA8_TIMING
+#define FA8_T(var) var = clock64()
+#else
+#define FA8_T(var)
+#endif
+
+// One pass over the 64 scores of this thread's row in one S buffer:
+// P = 2^(c*s + neg_mc), packed to e4m3 into pk[16] (four per word, ascending key
+// index); returns the fp32 sum of P.  Columns >= lim are masked.
+//
+// kAllowFma: the pairs selected by FA8_POLY_PAIR_MASK evaluate 2^x on the FMA pipe:
+//   y  = sat(s*c/128 + (neg_mc + 120)/128)     x = 128y - 120 clamped to [-120, 8]
+//   t  = 128y + (M - 120),  M = 1.5*2^23       t = M + n, n = round(x)
+//   f  = 128y - (t - (M - 120)) = x - n        |f| <= 1/2
+//   2^x = poly3(f) * 2^n                       cubic minimax, rel. error 7.5e-5; the
+//                                              exponent is added in the integer domain
+// A value clamped from above reads 2^8 > kLazyLimit, so the caller's overflow test
+// still fires.
+template <bool kAllowFma>
+__device__ __forceinline__ float softmax_pass(uint32_t t_s, int lim, float c, float neg_mc,
+                                              uint32_t (&pk)[16], long long& t_ld) {
+  constexpr float kMagic = 12582912.f, kMagicP = 12582912.f - 120.f;
+  const f32x2_t c2 = pack2(c, c), nm2 = pack2(neg_mc, neg_mc);
+  const float c128 = c * (1.f / 128.f), nm128 = (neg_mc + 120.f) * (1.f / 128.f);
+  const f32x2_t k128 = pack2(128.f, 128.f), magicp2 = pack2(kMagicP, kMagicP);
+  const f32x2_t neg1 = pack2(-1.f, -1.f);
+  const f32x2_t pc3 = pack2(0.055171654f, 0.055171654f), pc2 = pack2(0.24261114f, 0.24261114f);
+  const f32x2_t pc1 = pack2(0.69326097f, 0.69326097f), pc0 = pack2(0.99992806f, 0.99992806f);
+  (void)kMagic;
+  f32x2_t ls[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+  uint32_t sr[2][32];
+  tmem_ld_32x32b_x32(t_s, sr[0]);
+  tmem_ld_32x32b_x32(t_s + 32, sr[1]);
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    if (q == 0) { tmem_wait_ld(); FA8_T(t_ld); }
+    uint32_t (&s)[32] = sr[q];
+    if (lim < kSubN) {
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        if (q * 32 + e >= lim) s[e] = 0xff800000u;   // -inf
+    }
+#pragma unroll
+    for (int e = 0; e < 32; e += 4) {
+      float p[4];
+#pragma unroll
+      for (int u = 0; u < 4; u += 2) {
+        const float s0 = __uint_as_float(s[e + u]), s1 = __uint_as_float(s[e + u + 1]);
+        const bool on_fma = kAllowFma && (((FA8_POLY_PAIR_MASK) >> ((e + u) / 2)) & 1);
+        if (on_fma) {
+          const f32x2_t y2 = pack2(fma_sat(s0, c128, nm128), fma_sat(s1, c128, nm128));
+          const f32x2_t t2 = fma2(y2, k128, magicp2);
+          const f32x2_t nneg2 = fma2(t2, neg1, magicp2);          // -(n + 120)
+          const f32x2_t f2 = fma2(y2, k128, nneg2);
+          f32x2_t r2 = fma2(f2, pc3, pc2);
+          r2 = fma2(r2, f2, pc1);
+          r2 = fma2(r2, f2, pc0);
+          float r0, r1, t0, t1;
+          unpack2(r2, r0, r1);
+          unpack2(t2, t0, t1);
+          p[u] = __int_as_float(__float_as_int(r0) + (__float_as_int(t0) << 23));
+          p[u + 1] = __int_as_float(__float_as_int(r1) + (__float_as_int(t1) << 23));
+        } else {
+          float x0, x1;
+          unpack2(fma2(pack2(s0, s1), c2, nm2), x0, x1);
+          p[u] = ex2_approx(x0);
+          p[u + 1] = ex2_approx(x1);
+        }
+        ls[u >> 1] = add2(ls[u >> 1], pack2(p[u], p[u + 1]));
+      }
+      pk[q * 8 + e / 4] = pack_e4m3x4(p[0], p[1], p[2], p[3]);
+    }
+  }
+  float a0, a1, a2, a3;
+  unpack2(ls[0], a0, a1);
+  unpack2(ls[1], a2, a3);
+  return (a0 + a1) + (a2 + a3);
+}
+
+// Maximum of the (masked) 64 scores of this thread's row in one S buffer.
+__device__ __forceinline__ float row_max(uint32_t t_s, int lim) {
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    uint32_t s[32];
+    tmem_ld_32x32b_x32(t_s + 32 * q, s);
+    tmem_wait_ld();
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      const float v = (q * 32 + e < lim) ? __uint_as_float(s[e]) : -INFINITY;
+      mx[e & 3] = fmaxf(mx[e & 3], v);
+    }
+  }
+  return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+}
+
 }  // namespace
 
 template <int D, bool kCausal>
@@ -124,9 +238,16 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   auto bar_q_full = [&](int i) { return s_bar + 8u * i; };
   auto bar_kv_full = [&](int s) { return s_bar + 8u * (2 + s); };
   auto bar_kv_empty = [&](int s) { return s_bar + 8u * (2 + C::kSlots + s); };
-  auto bar_s_full = [&](int i) { return s_bar + 8u * (2 + 2 * C::kSlots + i); };
-  auto bar_p_full = [&](int i) { return s_bar + 8u * (4 + 2 * C::kSlots + i); };
-  const uint32_t bar_drain = s_bar + 8u * (6 + 2 * C::kSlots);
+  auto bar_s_full = [&](int i, int h) { return s_bar + 8u * (2 + 2 * C::kSlots + 2 * i + h); };
+  // One P barrier per S buffer: a softmax warp may run one sub-block ahead of its
+  // siblings (the next S is already there), never two.
+  auto bar_p_full = [&](int i, int h) { return s_bar + 8u * (6 + 2 * C::kSlots + 2 * i + h); };
+  auto bar_o_done = [&](int i) { return s_bar + 8u * (10 + 2 * C::kSlots + i); };
+  // Completes once, after the last PV of tile i.  (The epilogue cannot use o_done: a warp
+  // that ran ahead of its siblings may get there two phases early, which a parity wait
+  // cannot tell from "done".)
+  auto bar_o_final = [&](int i) { return s_bar + 8u * (12 + 2 * C::kSlots + i); };
+  const uint32_t bar_drain = s_bar + 8u * (14 + 2 * C::kSlots);
   volatile uint32_t* tmem_ptr_slot =
       reinterpret_cast<volatile uint32_t*>(smem_gen + C::kBarOffset + C::kNumBars * 8);
   volatile int* abort_flag =
@@ -139,36 +260,40 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int pair = kCausal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
   const int bh = blockIdx.y;
   const int row0 = pair * 2 * kTileM;                 // first query row of tile 0
-  const int nb_all = (seqlen + kBlockN - 1) / kBlockN;
-  // Number of key blocks each tile visits (0 = the tile lies past the end).
-  int nb_t[2];
+  // Number of 64-position sub-blocks each tile visits (0 = the tile lies past the end).
+  int nsb_t[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int r0 = row0 + i * kTileM;
-    int nb = 0;
+    int n = 0;
     if (r0 < seqlen) {
-      nb = nb_all;
-      if (kCausal) {
-        const int last_row = min(r0 + kTileM, seqlen) - 1;
-        nb = min(nb_all, last_row / kBlockN + 1);
-      }
+      const int col_end = kCausal ? min(r0 + kTileM, seqlen) : seqlen;   // one past the last visible key
+      n = (col_end + kSubN - 1) / kSubN;
     }
-    nb_t[i] = nb;
+    nsb_t[i] = n;
   }
-  const int nb = max(nb_t[0], nb_t[1]);
+  const int nsb = max(nsb_t[0], nsb_t[1]);
+  const int nb = (nsb + 1) / 2;                       // K/V tiles to load
 
   const WaitCtx wctx{abort_flag, args.status, args.timeout_ns};
 
   if (threadIdx.x == 0) {
-    *abort_flag = 0;
+    // A status word that is already non-zero (an earlier CTA of this launch gave up, or the
+    // caller did not clear it) makes the CTA return at once: a failed launch then costs one
+    // wait limit, not one per wave of CTAs.
+    *abort_flag = (args.status != nullptr && *reinterpret_cast<volatile int*>(args.status) != 0) ? 2 : 0;
     for (int i = 0; i < 2; ++i) mbar_init(bar_q_full(i), 1);
     for (int s = 0; s < C::kSlots; ++s) {
       mbar_init(bar_kv_full(s), 1);
       mbar_init(bar_kv_empty(s), 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar_s_full(i), 1);
-      mbar_init(bar_p_full(i), kTileM);
+      mbar_init(bar_s_full(i, 0), 1);
+      mbar_init(bar_s_full(i, 1), 1);
+      mbar_init(bar_p_full(i, 0), 4);   // one arrive per softmax warp
+      mbar_init(bar_p_full(i, 1), 4);
+      mbar_init(bar_o_done(i), 1);
+      mbar_init(bar_o_final(i), 1);
     }
     mbar_init(bar_drain, 1);
     fence_mbar_init();
@@ -182,8 +307,12 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
+  const bool skip_cta = (*abort_flag == 2);
+  __syncthreads();            // nobody raises the flag before everyone has read it
 
-  if (warp == kLoadWarp) {
+  if (skip_cta) {
+    // fall through to the teardown
+  } else if (warp == kLoadWarp) {
     // ------------------------------------------------------------ TMA producer
     if (elect_one()) {
       prefetch_tensormap(&tm_q);
@@ -204,7 +333,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       load_kv(&tm_k, 0, 0);
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        if (nb_t[i] > 0) {
+        if (nsb_t[i] > 0) {
           mbar_arrive_expect_tx(bar_q_full(i), C::kTileBytes);
           tma_load_3d(s_q + i * C::kTileBytes, &tm_q, bar_q_full(i), 0, row0 + i * kTileM, bh);
         }
@@ -227,7 +356,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-          if (nb_t[i] > 0) {
+          if (nsb_t[i] > 0) {
             const uint64_t t0 = global_timer_ns();
             while (!mbar_try_wait(bar_q_full(i), 0)) {
               if (global_timer_ns() - t0 > 20000000ull) break;
@@ -240,7 +369,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else if (warp == kMmaWarp) {
     // -------------------------------------------------------------- MMA issuer
     if (elect_one()) {
-      constexpr uint32_t kIdescQK = umma_idesc(kTileM, kBlockN);
+      constexpr uint32_t kIdescQK = umma_idesc(kTileM, kSubN);
       constexpr uint32_t kIdescPV = umma_idesc(kTileM, D);
       bool ok = true;
       auto slot_of = [&](int load) { return load % C::kSlots; };
@@ -248,59 +377,75 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       auto wait_load = [&](int load) {
         if (ok) ok = wait_bounded(wctx, bar_kv_full(slot_of(load)), parity_of(load), 0x200 + slot_of(load));
       };
-      // S_i = Q_i K^T: D/32 steps of K=32 bytes along the swizzled rows.
-      auto issue_qk = [&](int i, int load) {
+      // S_i[h] = Q_i K_sb^T for sub-block sb = 2j+h: rows 64h..64h+63 of tile K_j;
+      // D/32 steps of K=32 bytes along the swizzled rows.
+      auto issue_qk = [&](int i, int h, int load) {
         const uint64_t dq = umma_desc(s_q + i * C::kTileBytes, C::kQKSbo, C::kQKLayout);
-        const uint64_t dk = umma_desc(s_ring + slot_of(load) * C::kTileBytes, C::kQKSbo, C::kQKLayout);
+        const uint64_t dk = umma_desc(s_ring + slot_of(load) * C::kTileBytes + h * kSubN * D,
+                                      C::kQKSbo, C::kQKLayout);
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
-          mma_f8_ss(tmem_base + i * kBlockN, dq + 2u * k, dk + 2u * k, kIdescQK, k > 0);
+          mma_f8_ss(tmem_base + i * kBlockN + h * kSubN, dq + 2u * k, dk + 2u * k, kIdescQK, k > 0);
       };
-      // O_i (+)= P_i V: P is 128 rows x 128 e4m3 = 32 TMEM columns over S_i;
-      // V^T tile is D rows of 128 key positions (K-major, 128-byte swizzle).
-      auto issue_pv = [&](int i, int load, bool acc) {
+      // O_i (+)= P_i(sb) V_sb: P is 128 rows x 64 e4m3 = 16 TMEM columns over S_i[h];
+      // the V^T tile is D rows of 128 key positions (K-major, 128-byte swizzle), of which
+      // sub-block h covers bytes 64h..64h+63 of every row = K-steps 2h and 2h+1.
+      auto issue_pv = [&](int i, int h, int load, bool acc) {
         const uint64_t dv = umma_desc(s_ring + slot_of(load) * C::kTileBytes, 1024u, 2u);
 #pragma unroll
-        for (int k = 0; k < kBlockN / 32; ++k)
-          mma_f8_ts(tmem_base + kTmemO + i * D, tmem_base + i * kBlockN + 8u * k, dv + 2u * k,
-                    kIdescPV, (acc || k > 0) ? 1u : 0u);
+        for (int k = 0; k < kSubN / 32; ++k)
+          mma_f8_ts(tmem_base + kTmemO + i * D, tmem_base + i * kBlockN + h * kSubN + 8u * k,
+                    dv + 2u * (2 * h + k), kIdescPV, (acc || k > 0) ? 1u : 0u);
       };
 
       wait_load(0);
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        if (nb_t[i] > 0) {
+        if (nsb_t[i] > 0) {
           if (ok) ok = wait_bounded(wctx, bar_q_full(i), 0, 0x300 + i);
           if (ok) {
             tc_fence_after();
-            issue_qk(i, 0);
-            tc_commit(bar_s_full(i));
+            issue_qk(i, 0, 0);
+            tc_commit(bar_s_full(i, 0));
           }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        if (nsb_t[i] > 1 && ok) {
+          issue_qk(i, 1, 0);
+          tc_commit(bar_s_full(i, 1));
         }
       }
       if (ok) tc_commit(bar_kv_empty(slot_of(0)));
 
-      for (int j = 0; j < nb && ok; ++j) {
-        const int ld_v = 2 * j + 1, ld_k = 2 * j + 2;
-        const bool has_next = (j + 1 < nb);
-        wait_load(ld_v);
-        if (has_next) wait_load(ld_k);
+      for (int sb = 0; sb < nsb && ok; ++sb) {
+        const int j = sb >> 1, h = sb & 1;
+        const int ld_v = 2 * j + 1, ld_kn = 2 * j + 2;      // V_j and K_{j+1}
+        const bool kn_loaded = (2 * j + 2 < nsb);
+        if (h == 0) {
+          wait_load(ld_v);
+          if (kn_loaded) wait_load(ld_kn);
+        }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-          if (j < nb_t[i]) {
-            if (ok) ok = wait_bounded(wctx, bar_p_full(i), static_cast<uint32_t>(j) & 1u, 0x400 + i);
+          if (sb < nsb_t[i]) {
+            if (ok) ok = wait_bounded(wctx, bar_p_full(i, h), static_cast<uint32_t>(sb >> 1) & 1u, 0x400 + i);
             if (ok) {
               tc_fence_after();
-              issue_pv(i, ld_v, j > 0);
-              if (j + 1 < nb_t[i]) issue_qk(i, ld_k);
-              // Arrives when PV_i(j) (and S_i(j+1), if issued) are complete.
-              tc_commit(bar_s_full(i));
+              issue_pv(i, h, ld_v, sb > 0);
+              tc_commit(bar_o_done(i));                    // phase sb: PV_i(0..sb) complete
+              if (sb == nsb_t[i] - 1) tc_commit(bar_o_final(i));
+              if (sb + 2 < nsb_t[i]) {
+                issue_qk(i, h, ld_kn);
+                tc_commit(bar_s_full(i, h));               // S_i[h] now holds sub-block sb+2
+              }
             }
           }
         }
-        if (ok) {
+        if (ok && (h == 1 || sb == nsb - 1)) {
           tc_commit(bar_kv_empty(slot_of(ld_v)));
-          if (has_next) tc_commit(bar_kv_empty(slot_of(ld_k)));
+          if (h == 1 && kn_loaded) tc_commit(bar_kv_empty(slot_of(ld_kn)));
         }
       }
       if (!ok) {
@@ -321,47 +466,50 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t t_s = tmem_base + lane_sel + i * kBlockN;
     const uint32_t t_o = tmem_base + lane_sel + kTmemO + i * D;
     const int q_row = row0 + i * kTileM + row;         // global query row, may be >= seqlen
-    const int my_nb = nb_t[i];
+    const int my_nsb = nsb_t[i];
+    const int col_lim = kCausal ? min(seqlen, q_row + 1) : seqlen;   // keys this row may see
     const float c = args.scale_log2;
+    // m is the row maximum the exponentials are taken against: exact after the first
+    // sub-block, then raised only by the exact path below.  l and O are sums against
+    // the same m, so O/l does not depend on when m is raised.
     float m = -INFINITY, l = 0.f;
     bool ok = true;
 
-    for (int j = 0; j < my_nb; ++j) {
-      ok = wait_bounded(wctx, bar_s_full(i), static_cast<uint32_t>(j) & 1u, 0x500 + i);
+    long long tt0 = 0, tt1 = 0, tt_ld = 0, tt2 = 0, tt3 = 0, tt4 = 0;
+    long long acc_wait = 0, acc_ld = 0, acc_math = 0, acc_st = 0, acc_arr = 0;
+    (void)tt0; (void)tt1; (void)tt_ld; (void)tt2; (void)tt3; (void)tt4;
+    for (int sb = 0; sb < my_nsb; ++sb) {
+      const int h = sb & 1;
+      FA8_T(tt0);
+      ok = wait_bounded(wctx, bar_s_full(i, h), static_cast<uint32_t>(sb >> 1) & 1u, 0x500 + i);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      FA8_T(tt1);
+      const uint32_t t_sb = t_s + h * kSubN;
+      const int lim = col_lim - sb * kSubN;            // sub-block-local first masked column
 
-      uint32_t sr[4][32];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) tmem_ld_32x32b_x32(t_s + 32 * q, sr[q]);
-      tmem_wait_ld();
-
-      // Columns at or past `lim` (block-local) are masked: end of the sequence,
-      // and for causal attention everything right of the diagonal.
-      int lim = seqlen - j * kBlockN;
-      if (kCausal) lim = min(lim, q_row + 1 - j * kBlockN);
-      if (lim < kBlockN) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (q * 32 + e >= lim) sr[q][e] = 0xff800000u;   // -inf
+      uint32_t pk[16];
+      float bsum = 0.f;
+      bool exact = (sb == 0);
+      if (!exact) {
+        // Fast path: one pass, exponentials against the stale maximum.
+        bsum = softmax_pass<true>(t_sb, lim, c, -m * c, pk, tt_ld);
+        // Some P above kLazyLimit implies a sum above it (all P >= 0); a false alarm
+        // only costs the exact path.
+        exact = __any_sync(0xffffffffu, !(bsum <= kLazyLimit));
       }
-
-      float mx[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        mx[q] = __uint_as_float(sr[q][0]);
-#pragma unroll
-        for (int e = 1; e < 32; ++e) mx[q] = fmaxf(mx[q], __uint_as_float(sr[q][e]));
-      }
-      const float m_new = fmaxf(fmaxf(m, fmaxf(mx[0], mx[1])), fmaxf(mx[2], mx[3]));
-
-      if (j > 0) {
-        // The commit that completed this phase also covered PV_i(j-1), so O_i is
-        // quiescent here; PV_i(j) is not issued before this thread's arrive below.
-        if (__any_sync(0xffffffffu, m_new > m)) {
+      if (exact) {
+        // Exact path (first sub-block, or the stale maximum is too low for some row
+        // of this warp): true row maximum, rescale l and O, redo the exponentials.
+        const float m_new = fmaxf(m, row_max(t_sb, lim));
+        if (sb > 0) {
+          // O_i must be quiescent: PV_i(sb-1) complete (PV_i(sb) is not issued before
+          // this warp's arrive below).
+          ok = wait_bounded(wctx, bar_o_done(i), static_cast<uint32_t>(sb - 1) & 1u, 0x700 + i);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
           float alpha = ex2_approx((m - m_new) * c);
           if (m == -INFINITY) alpha = 1.f;
           l *= alpha;
@@ -375,36 +523,31 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             tmem_st_32x32b_x32(t_o + 32 * q, orow);
           }
         }
+        m = m_new;
+        bsum = softmax_pass<false>(t_sb, lim, c, (m == -INFINITY) ? 0.f : -m * c, pk, tt_ld);
       }
-      m = m_new;
-      const float neg_mc = (m == -INFINITY) ? 0.f : -m * c;
-
-      uint32_t pk[32];
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sr[q][e + 0]), c, neg_mc));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sr[q][e + 1]), c, neg_mc));
-          const float p2 = ex2_approx(fmaf(__uint_as_float(sr[q][e + 2]), c, neg_mc));
-          const float p3 = ex2_approx(fmaf(__uint_as_float(sr[q][e + 3]), c, neg_mc));
-          ls[0] += p0;
-          ls[1] += p1;
-          ls[2] += p2;
-          ls[3] += p3;
-          pk[q * 8 + e / 4] = pack_e4m3x4(p0, p1, p2, p3);
-        }
-      }
-      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      tmem_st_32x32b_x32(t_s, pk);
+      l += bsum;
+      FA8_T(tt2);
+      tmem_st_32x32b_x16(t_sb, pk);
       tmem_wait_st();
+      FA8_T(tt3);
       tc_fence_before();
-      mbar_arrive(bar_p_full(i));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p_full(i, h));
+      FA8_T(tt4);
+#ifdef FA8_TIMING
+      if (sb > 0) { acc_wait += tt1 - tt0; acc_ld += tt_ld - tt1; acc_math += tt2 - tt_ld; acc_st += tt3 - tt2; acc_arr += tt4 - tt3; }
+#endif
     }
+#ifdef FA8_TIMING
+    if (args.dbg != nullptr && blockIdx.x == 1 && blockIdx.y == 3 && lane == 0) {
+      long long* d = args.dbg + warp * 8;
+      d[0] = acc_wait; d[1] = acc_ld; d[2] = acc_math; d[3] = acc_st; d[4] = acc_arr; d[5] = my_nsb - 1;
+    }
+#endif
 
-    if (ok && my_nb > 0) {
-      ok = wait_bounded(wctx, bar_s_full(i), static_cast<uint32_t>(my_nb) & 1u, 0x600 + i);
+    if (ok && my_nsb > 0) {
+      ok = wait_bounded(wctx, bar_o_final(i), 0, 0x600 + i);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();

@@ -142,10 +142,18 @@ def attention_reference_fp16(q8, k8, v8, causal: bool, softmax_scale: float) -> 
 
 
 def attention_quantised_p(q8, k8, v8, causal: bool, softmax_scale: float, block_n: int = 128,
-                          o_scale: float = 1.0) -> torch.Tensor:
+                          o_scale: float = 1.0, lazy: bool = False, lazy_limit: float = 256.0,
+                          lazy_rows: int = 32) -> torch.Tensor:
     """Model of an FP8 kernel (see module docstring).  Raw e4m3 values are used
     as they are (no descale), like the reference kernel.  Returns fp32 [B,H,S,D]
-    *before* any rounding of O."""
+    *before* any rounding of O.
+
+    lazy=False is the reference's rule: the running maximum m follows every block
+    (csrc/flash_attention.cu:233-273), so P <= 1.  lazy=True models the sm_100a
+    kernel: after the first block m is kept until, within a group of `lazy_rows`
+    consecutive query rows, some row's block sum of P exceeds `lazy_limit`; only then
+    m, l and the accumulator of the whole group are brought up to date.  Both give the
+    same O/l up to the rounding of P."""
     q = _as_f32(q8)
     k = _as_f32(k8)
     v = _as_f32(v8)
@@ -164,6 +172,13 @@ def attention_quantised_p(q8, k8, v8, causal: bool, softmax_scale: float, block_
                     cols = torch.arange(n0, n1).unsqueeze(0)
                     s = s.masked_fill(cols > rows, float("-inf"))
                 m_new = torch.maximum(m, s.max(dim=1).values)
+                if lazy and n0 > 0:
+                    p_stale = torch.exp(s * softmax_scale - (m * softmax_scale).unsqueeze(1))
+                    over = ~(p_stale.sum(dim=1) <= lazy_limit)
+                    pad = (-S) % lazy_rows
+                    grp = torch.cat([over, torch.zeros(pad, dtype=torch.bool)]).view(-1, lazy_rows).any(dim=1)
+                    update = grp.repeat_interleave(lazy_rows)[:S]
+                    m_new = torch.where(update, m_new, m)
                 alpha = torch.where(torch.isinf(m) & (m < 0), torch.ones_like(m),
                                     torch.exp((m - m_new) * softmax_scale))
                 m_eff = torch.where(torch.isinf(m_new), torch.zeros_like(m_new), m_new)
