@@ -125,15 +125,6 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   args.o_scale = p->o_scale;
   args.status = p->status_word;
   args.timeout_ns = 2000000000ull;
-#ifdef FA8_TIMING
-  // debug builds: the status word doubles as a pointer carrier (first 8 bytes hold the address)
-  args.dbg = nullptr;
-  if (p->status_word) {
-    long long addr = 0;
-    cudaMemcpy(&addr, reinterpret_cast<const char*>(p->status_word) + 8, 8, cudaMemcpyDeviceToHost);
-    args.dbg = reinterpret_cast<long long*>(addr);
-  }
-#endif
   const int n_pairs = (p->seqlen + 255) / 256;
   cudaError_t e = fa8::launch_fwd(p->head_dim, p->is_causal != 0, tq, tk, tv, args, n_pairs,
                                   static_cast<int>(bh), static_cast<cudaStream_t>(cuda_stream));

@@ -11,17 +11,21 @@
 // tensor memory and its next S = Q K^T is computed while the softmax of the
 // current sub-block is still running:
 //
-//   warp 9      TMA producer: Q tiles once, then K_j / V_j tiles into a ring of
+//   warp 17     TMA producer: Q tiles once, then K_j / V_j tiles into a ring of
 //               shared-memory slots, each guarded by a full/empty mbarrier pair.
-//   warp 8      MMA issuer (one elected lane): S_i[sb&1] = Q_i K_sb^T (M128 N64)
+//   warp 16     MMA issuer (one elected lane): S_i[sb&1] = Q_i K_sb^T (M128 N64)
 //               and O_i += P_i(sb) V_sb (M128 N=head_dim) as tcgen05.mma
 //               kind::f8f6f4 with fp32 accumulators in tensor memory; completion
 //               is signalled with tcgen05.commit on mbarriers.
-//   warps 0-3   online softmax for query tile 0 (one TMEM lane = one row per
-//   warps 4-7   thread), resp. tile 1: exp2 with the scale folded in, row sum from
-//               the fp32 probabilities, P re-quantised to e4m3 and written back to
-//               TMEM over its own S buffer as the A operand of the second GEMM;
-//               fp32 rescale of O in TMEM when the row maximum has to be raised.
+//   warps 0-7   online softmax for query tile 0, warps 8-15 for tile 1.  A TMEM lane
+//               is a query row (tcgen05.ld 32x32b: one row per thread, no shuffles).
+//               Warps w and w+4 of a tile own the same 32 rows: the first takes the
+//               even sub-blocks (S buffer 0), the second the odd ones (S buffer 1),
+//               so four softmax warps per scheduler keep the special-function and
+//               FMA pipes fed.  exp2 with the scale folded in, row sum from the fp32
+//               probabilities, P re-quantised to e4m3 and written back to TMEM over
+//               its own S buffer as the A operand of the second GEMM; fp32 rescale of
+//               O in TMEM when the row maximum has to be raised.
 //
 // TMEM columns: tile i has S buffers at 128*i and 128*i+64 (64 fp32 columns each;
 // P, 64 e4m3 = 16 columns, overlays the buffer it was computed from) and O_i at
@@ -55,9 +59,9 @@ namespace {
 constexpr int kTileM = 128;        // query rows per tile = TMEM lanes
 constexpr int kBlockN = 128;       // key/value positions per TMA tile
 constexpr int kSubN = 64;          // key/value positions per MMA / softmax sub-block
-constexpr int kMmaWarp = 8;
-constexpr int kLoadWarp = 9;
-constexpr int kThreads = 320;
+constexpr int kMmaWarp = 16;
+constexpr int kLoadWarp = 17;
+constexpr int kThreads = 576;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemO = 256;   // first O column; S_0 at 0, S_1 at 128
 
@@ -69,8 +73,10 @@ struct Cfg {
   static constexpr int kQBytes = 2 * kTileBytes;
   static constexpr int kRingBytes = kSlots * kTileBytes;
   static constexpr int kBarOffset = kQBytes + kRingBytes;
+  // row-group scratch shared by the two warps of a 32-row group, see RowGroupShared
+  static constexpr int kGroupBytes = 8 * 672;
   static constexpr int kNumBars = 2 /*q_full*/ + 2 * kSlots + 4 /*s_full*/ + 4 /*p_full*/ + 2 /*o_done*/ + 2 /*o_final*/ + 1 /*drain*/;
-  static constexpr int kSmemBytes = kBarOffset + kNumBars * 8 + 16 /*tmem ptr, abort*/ + 1024 /*align*/;
+  static constexpr int kSmemBytes = kBarOffset + kNumBars * 8 + 16 /*tmem ptr, abort*/ + kGroupBytes + 1024 /*align*/;
   // Q and K rows are D bytes long: one 128-byte swizzle row for D=128, a 64-byte one for D=64.
   static constexpr uint32_t kQKLayout = (D == 128) ? 2u : 4u;   // UMMA SWIZZLE_128B / SWIZZLE_64B
   static constexpr uint32_t kQKSbo = 8 * D;                      // bytes between 8-row groups
@@ -119,21 +125,27 @@ __device__ __forceinline__ bool wait_bounded(const WaitCtx& w, uint32_t bar, uin
 // Which of the 16 element pairs of a 32-column chunk take their exponential on the FMA
 // pipe instead of the special-function unit (bit p = pair p).
 #ifndef FA8_POLY_PAIR_MASK
-#define FA8_POLY_PAIR_MASK 0x4925
+#define FA8_POLY_PAIR_MASK 0x1111
 #endif
 // P may grow to kLazyLimit (<= 448, the e4m3 maximum, with room for the polynomial
 // path's clamp at 2^8) before the row maximum is raised.
 constexpr float kLazyLimit = 128.f;
 
-#ifdef FA8_TIMING
-#define FA8_T(var) var = clock64()
-#else
-#define FA8_T(var)
-#endif
+// Four fp32 -> four e4m3 in one word (ascending index = ascending byte).
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+  uint32_t r;
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t}"
+      : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
+}
 
-// One pass over the 64 scores of this thread's row in one S buffer:
-// P = 2^(c*s + neg_mc), packed to e4m3 into pk[16] (four per word, ascending key
-// index); returns the fp32 sum of P.  Columns >= lim are masked.
+// One pass over 32 of the scores of this thread's row (TMEM columns t_cols..+31):
+// P = 2^(c*s + neg_mc), packed to e4m3 into pk[8] (four per word, ascending key
+// index); adds the fp32 P into the two packed accumulators ls[].  Columns >= lim
+// (relative to the first of the 32) are masked.
 //
 // kAllowFma: the pairs selected by FA8_POLY_PAIR_MASK evaluate 2^x on the FMA pipe:
 //   y  = sat(s*c/128 + (neg_mc + 120)/128)     x = 128y - 120 clamped to [-120, 8]
@@ -144,70 +156,72 @@ constexpr float kLazyLimit = 128.f;
 // A value clamped from above reads 2^8 > kLazyLimit, so the caller's overflow test
 // still fires.
 template <bool kAllowFma>
-__device__ __forceinline__ float softmax_pass(uint32_t t_s, int lim, float c, float neg_mc,
-                                              uint32_t (&pk)[16], long long& t_ld) {
-  constexpr float kMagic = 12582912.f, kMagicP = 12582912.f - 120.f;
+__device__ __forceinline__ void softmax_chunk(uint32_t t_cols, int lim, float c, float neg_mc,
+                                              uint32_t* pk, f32x2_t (&ls)[2]) {
   const f32x2_t c2 = pack2(c, c), nm2 = pack2(neg_mc, neg_mc);
   const float c128 = c * (1.f / 128.f), nm128 = (neg_mc + 120.f) * (1.f / 128.f);
-  const f32x2_t k128 = pack2(128.f, 128.f), magicp2 = pack2(kMagicP, kMagicP);
+  const f32x2_t k128 = pack2(128.f, 128.f);
+  const f32x2_t magicp2 = pack2(12582912.f - 120.f, 12582912.f - 120.f);
   const f32x2_t neg1 = pack2(-1.f, -1.f);
   const f32x2_t pc3 = pack2(0.055171654f, 0.055171654f), pc2 = pack2(0.24261114f, 0.24261114f);
   const f32x2_t pc1 = pack2(0.69326097f, 0.69326097f), pc0 = pack2(0.99992806f, 0.99992806f);
-  (void)kMagic;
-  f32x2_t ls[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
-  uint32_t sr[2][32];
-  tmem_ld_32x32b_x32(t_s, sr[0]);
-  tmem_ld_32x32b_x32(t_s + 32, sr[1]);
+  uint32_t s[32];
+  tmem_ld_32x32b_x32(t_cols, s);
+  tmem_wait_ld();
+  if (lim < 32) {
 #pragma unroll
-  for (int q = 0; q < 2; ++q) {
-    if (q == 0) { tmem_wait_ld(); FA8_T(t_ld); }
-    uint32_t (&s)[32] = sr[q];
-    if (lim < kSubN) {
-#pragma unroll
-      for (int e = 0; e < 32; ++e)
-        if (q * 32 + e >= lim) s[e] = 0xff800000u;   // -inf
-    }
-#pragma unroll
-    for (int e = 0; e < 32; e += 4) {
-      float p[4];
-#pragma unroll
-      for (int u = 0; u < 4; u += 2) {
-        const float s0 = __uint_as_float(s[e + u]), s1 = __uint_as_float(s[e + u + 1]);
-        const bool on_fma = kAllowFma && (((FA8_POLY_PAIR_MASK) >> ((e + u) / 2)) & 1);
-        if (on_fma) {
-          const f32x2_t y2 = pack2(fma_sat(s0, c128, nm128), fma_sat(s1, c128, nm128));
-          const f32x2_t t2 = fma2(y2, k128, magicp2);
-          const f32x2_t nneg2 = fma2(t2, neg1, magicp2);          // -(n + 120)
-          const f32x2_t f2 = fma2(y2, k128, nneg2);
-          f32x2_t r2 = fma2(f2, pc3, pc2);
-          r2 = fma2(r2, f2, pc1);
-          r2 = fma2(r2, f2, pc0);
-          float r0, r1, t0, t1;
-          unpack2(r2, r0, r1);
-          unpack2(t2, t0, t1);
-          p[u] = __int_as_float(__float_as_int(r0) + (__float_as_int(t0) << 23));
-          p[u + 1] = __int_as_float(__float_as_int(r1) + (__float_as_int(t1) << 23));
-        } else {
-          float x0, x1;
-          unpack2(fma2(pack2(s0, s1), c2, nm2), x0, x1);
-          p[u] = ex2_approx(x0);
-          p[u + 1] = ex2_approx(x1);
-        }
-        ls[u >> 1] = add2(ls[u >> 1], pack2(p[u], p[u + 1]));
-      }
-      pk[q * 8 + e / 4] = pack_e4m3x4(p[0], p[1], p[2], p[3]);
-    }
+    for (int e = 0; e < 32; ++e)
+      if (e >= lim) s[e] = 0xff800000u;   // -inf
   }
+#pragma unroll
+  for (int e = 0; e < 32; e += 4) {
+    float p[4];
+#pragma unroll
+    for (int u = 0; u < 4; u += 2) {
+      const float s0 = __uint_as_float(s[e + u]), s1 = __uint_as_float(s[e + u + 1]);
+      const bool on_fma = kAllowFma && (((FA8_POLY_PAIR_MASK) >> ((e + u) / 2)) & 1);
+      if (on_fma) {
+        const f32x2_t y2 = pack2(fma_sat(s0, c128, nm128), fma_sat(s1, c128, nm128));
+        const f32x2_t t2 = fma2(y2, k128, magicp2);
+        const f32x2_t nneg2 = fma2(t2, neg1, magicp2);          // -(n + 120)
+        const f32x2_t f2 = fma2(y2, k128, nneg2);
+        f32x2_t r2 = fma2(f2, pc3, pc2);
+        r2 = fma2(r2, f2, pc1);
+        r2 = fma2(r2, f2, pc0);
+        float r0, r1, t0, t1;
+        unpack2(r2, r0, r1);
+        unpack2(t2, t0, t1);
+        p[u] = __int_as_float(__float_as_int(r0) + (__float_as_int(t0) << 23));
+        p[u + 1] = __int_as_float(__float_as_int(r1) + (__float_as_int(t1) << 23));
+      } else {
+        float x0, x1;
+        unpack2(fma2(pack2(s0, s1), c2, nm2), x0, x1);
+        p[u] = ex2_approx(x0);
+        p[u + 1] = ex2_approx(x1);
+      }
+      ls[u >> 1] = add2(ls[u >> 1], pack2(p[u], p[u + 1]));
+    }
+    pk[e / 4] = pack4_e4m3(p[0], p[1], p[2], p[3]);
+  }
+}
+
+// P of one 64-key sub-block of this thread's row -> pk[16]; returns the fp32 row sum.
+template <bool kAllowFma>
+__device__ __forceinline__ float softmax_pass(uint32_t t_sb, int lim, float c, float neg_mc,
+                                              uint32_t (&pk)[16]) {
+  f32x2_t ls[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+  softmax_chunk<kAllowFma>(t_sb, lim, c, neg_mc, pk, ls);
+  softmax_chunk<kAllowFma>(t_sb + 32, lim - 32, c, neg_mc, pk + 8, ls);
   float a0, a1, a2, a3;
   unpack2(ls[0], a0, a1);
   unpack2(ls[1], a2, a3);
   return (a0 + a1) + (a2 + a3);
 }
 
-// Maximum of the (masked) 64 scores of this thread's row in one S buffer.
-__device__ __forceinline__ float row_max(uint32_t t_s, int lim) {
+// Maximum of the (masked) 64 scores of this thread's row in one S buffer.  Out of line:
+// it runs once per tile plus whenever a row maximum has to be raised.
+__device__ __noinline__ float row_max(uint32_t t_s, int lim) {
   float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
   for (int q = 0; q < 2; ++q) {
     uint32_t s[32];
     tmem_ld_32x32b_x32(t_s + 32 * q, s);
@@ -220,6 +234,33 @@ __device__ __forceinline__ float row_max(uint32_t t_s, int lim) {
   }
   return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 }
+
+// Multiplies `chunks` x 32 fp32 columns of this thread's TMEM lane by alpha (the rare
+// rescale of O when a row maximum is raised).  Out of line so that its registers do not
+// weigh on the softmax loop.
+__device__ __noinline__ void rescale_o_columns(uint32_t t_o, int chunks, float alpha) {
+  for (int q = 0; q < chunks; ++q) {
+    uint32_t orow[32];
+    tmem_ld_32x32b_x32(t_o + 32 * q, orow);
+    tmem_wait_ld();
+#pragma unroll
+    for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * alpha);
+    tmem_st_32x32b_x32(t_o + 32 * q, orow);
+  }
+  tmem_wait_st();
+}
+
+// What the two warps of a 32-row group share (672 bytes per group): the row maxima the
+// exponentials are taken against, a version counter bumped whenever they are raised,
+// and each warp's final (row sum, maximum it refers to) for the epilogue.
+struct RowGroupShared {
+  volatile float m[32];
+  volatile uint32_t version;
+  uint32_t pad[7];
+  volatile float l_part[2][32];
+  volatile float m_part[2][32];
+};
+static_assert(sizeof(RowGroupShared) == 672, "RowGroupShared layout");
 
 }  // namespace
 
@@ -252,6 +293,8 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       reinterpret_cast<volatile uint32_t*>(smem_gen + C::kBarOffset + C::kNumBars * 8);
   volatile int* abort_flag =
       reinterpret_cast<volatile int*>(smem_gen + C::kBarOffset + C::kNumBars * 8 + 4);
+  RowGroupShared* groups =
+      reinterpret_cast<RowGroupShared*>(smem_gen + C::kBarOffset + C::kNumBars * 8 + 16);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -296,6 +339,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(bar_o_final(i), 1);
     }
     mbar_init(bar_drain, 1);
+    for (int g = 0; g < 8; ++g) groups[g].version = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -460,52 +504,77 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     __syncwarp();
   } else {
     // ------------------------------------------------- softmax + epilogue warps
-    const int i = warp >> 2;                           // query tile of this warpgroup
-    const int row = (warp & 3) * 32 + lane;            // row in the tile = TMEM lane
-    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_sel + i * kBlockN;
+    const int i = warp >> 3;                           // query tile of this warp
+    const int h = (warp >> 2) & 1;                     // S buffer = parity of my sub-blocks
+    const int quarter = warp & 3;                      // TMEM lane quarter = 32-row group
+    const int row = quarter * 32 + lane;               // row in the tile = TMEM lane
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t t_sb = tmem_base + lane_sel + i * kBlockN + h * kSubN;   // my S buffer
     const uint32_t t_o = tmem_base + lane_sel + kTmemO + i * D;
     const int q_row = row0 + i * kTileM + row;         // global query row, may be >= seqlen
-    const int my_nsb = nsb_t[i];
+    const int tile_nsb = nsb_t[i];
     const int col_lim = kCausal ? min(seqlen, q_row + 1) : seqlen;   // keys this row may see
     const float c = args.scale_log2;
-    // m is the row maximum the exponentials are taken against: exact after the first
-    // sub-block, then raised only by the exact path below.  l and O are sums against
-    // the same m, so O/l does not depend on when m is raised.
+    RowGroupShared& grp = groups[i * 4 + quarter];
+    // m is the row maximum the exponentials are taken against, shared by the two warps of
+    // the row group through grp.m / grp.version: exact after sub-block 0, then raised only
+    // by the exact path below.  l is this warp's share of the row sum, kept relative to m.
+    // O and both shares are sums against the same m, so O/l does not depend on when m is
+    // raised.
     float m = -INFINITY, l = 0.f;
+    uint32_t version = 0;
     bool ok = true;
 
-    long long tt0 = 0, tt1 = 0, tt_ld = 0, tt2 = 0, tt3 = 0, tt4 = 0;
-    long long acc_wait = 0, acc_ld = 0, acc_math = 0, acc_st = 0, acc_arr = 0;
-    (void)tt0; (void)tt1; (void)tt_ld; (void)tt2; (void)tt3; (void)tt4;
-    for (int sb = 0; sb < my_nsb; ++sb) {
-      const int h = sb & 1;
-      FA8_T(tt0);
-      ok = wait_bounded(wctx, bar_s_full(i, h), static_cast<uint32_t>(sb >> 1) & 1u, 0x500 + i);
+    // Brings m (and l with it) up to date with the partner's latest raise.
+    auto adopt = [&]() -> bool {
+      const uint32_t v = grp.version;
+      if (v == version) return false;
+      __threadfence_block();
+      const float m_new = grp.m[lane];
+      if (m != -INFINITY) l *= ex2_approx((m - m_new) * c);
+      m = m_new;
+      version = v;
+      return true;
+    };
+
+    for (int sb = h; sb < tile_nsb; sb += 2) {
+      const uint32_t ph = static_cast<uint32_t>(sb >> 1) & 1u;
+      ok = wait_bounded(wctx, bar_s_full(i, h), ph, 0x500 + i);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      FA8_T(tt1);
-      const uint32_t t_sb = t_s + h * kSubN;
       const int lim = col_lim - sb * kSubN;            // sub-block-local first masked column
 
       uint32_t pk[16];
       float bsum = 0.f;
+      const bool have_m = (version != 0);              // warp-uniform
+      if (have_m) {
+        // Fast path: one pass, exponentials against the maximum known so far.
+        bsum = softmax_pass<true>(t_sb, lim, c, -m * c, pk);
+      }
+      // P(sb) may be handed over only after the partner has handed over P(sb-1): from then
+      // on nobody else can raise the maximum before PV(sb) is issued.
+      if (sb > 0) {
+        ok = wait_bounded(wctx, bar_p_full(i, h ^ 1), static_cast<uint32_t>((sb - 1) >> 1) & 1u, 0x800 + i);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      bool redo = adopt() || !have_m;                  // warp-uniform: version is per group
+      redo = __any_sync(0xffffffffu, redo);
+      // Some P above kLazyLimit implies a sum above it (all P >= 0); a false alarm only
+      // costs the exact path.  Decided for the warp's 32 rows as a whole.
       bool exact = (sb == 0);
-      if (!exact) {
-        // Fast path: one pass, exponentials against the stale maximum.
-        bsum = softmax_pass<true>(t_sb, lim, c, -m * c, pk, tt_ld);
-        // Some P above kLazyLimit implies a sum above it (all P >= 0); a false alarm
-        // only costs the exact path.
+      if (!exact && !redo) exact = __any_sync(0xffffffffu, !(bsum <= kLazyLimit));
+      if (!exact && redo) {
+        bsum = softmax_pass<false>(t_sb, lim, c, -m * c, pk);
         exact = __any_sync(0xffffffffu, !(bsum <= kLazyLimit));
       }
       if (exact) {
-        // Exact path (first sub-block, or the stale maximum is too low for some row
-        // of this warp): true row maximum, rescale l and O, redo the exponentials.
+        // Exact path (first sub-block, or the maximum is too low for some row of this
+        // warp): true row maximum, rescale l and O, publish, redo the exponentials.
         const float m_new = fmaxf(m, row_max(t_sb, lim));
         if (sb > 0) {
-          // O_i must be quiescent: PV_i(sb-1) complete (PV_i(sb) is not issued before
-          // this warp's arrive below).
+          // O_i must be quiescent: PV_i(sb-1) complete; PV_i(sb) waits for this warp.
           ok = wait_bounded(wctx, bar_o_done(i), static_cast<uint32_t>(sb - 1) & 1u, 0x700 + i);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
@@ -513,50 +582,54 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           float alpha = ex2_approx((m - m_new) * c);
           if (m == -INFINITY) alpha = 1.f;
           l *= alpha;
-#pragma unroll
-          for (int q = 0; q < D / 32; ++q) {
-            uint32_t orow[32];
-            tmem_ld_32x32b_x32(t_o + 32 * q, orow);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * alpha);
-            tmem_st_32x32b_x32(t_o + 32 * q, orow);
-          }
+          rescale_o_columns(t_o, D / 32, alpha);
         }
         m = m_new;
-        bsum = softmax_pass<false>(t_sb, lim, c, (m == -INFINITY) ? 0.f : -m * c, pk, tt_ld);
+        grp.m[lane] = m_new;
+        __threadfence_block();
+        __syncwarp();
+        ++version;
+        if (lane == 0) grp.version = version;
+        bsum = softmax_pass<false>(t_sb, lim, c, (m == -INFINITY) ? 0.f : -m * c, pk);
       }
       l += bsum;
-      FA8_T(tt2);
+      if (sb + 2 >= tile_nsb) {                        // my last sub-block: leave my share for the epilogue
+        grp.l_part[h][lane] = l;
+        grp.m_part[h][lane] = m;
+        __threadfence_block();
+      }
       tmem_st_32x32b_x16(t_sb, pk);
       tmem_wait_st();
-      FA8_T(tt3);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p_full(i, h));
-      FA8_T(tt4);
-#ifdef FA8_TIMING
-      if (sb > 0) { acc_wait += tt1 - tt0; acc_ld += tt_ld - tt1; acc_math += tt2 - tt_ld; acc_st += tt3 - tt2; acc_arr += tt4 - tt3; }
-#endif
     }
-#ifdef FA8_TIMING
-    if (args.dbg != nullptr && blockIdx.x == 1 && blockIdx.y == 3 && lane == 0) {
-      long long* d = args.dbg + warp * 8;
-      d[0] = acc_wait; d[1] = acc_ld; d[2] = acc_math; d[3] = acc_st; d[4] = acc_arr; d[5] = my_nsb - 1;
-    }
-#endif
 
-    if (ok && my_nsb > 0) {
+    if (ok && tile_nsb > 0) {
       ok = wait_bounded(wctx, bar_o_final(i), 0, 0x600 + i);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();
-        const float inv = ((l == 0.f || l != l) ? 1.f : 1.f / l) * args.o_scale;
-        __half* o_row = args.o + (static_cast<size_t>(bh) * seqlen + q_row) * D;
+        __threadfence_block();
+        // Row sum = both warps' shares, each brought to the final maximum.
+        float l_tot = 0.f, m_fin = -INFINITY;
 #pragma unroll
-        for (int q = 0; q < D / 32; ++q) {
+        for (int w2 = 0; w2 < 2; ++w2)
+          if (w2 < tile_nsb) m_fin = fmaxf(m_fin, grp.m_part[w2][lane]);
+#pragma unroll
+        for (int w2 = 0; w2 < 2; ++w2) {
+          if (w2 < tile_nsb) {
+            const float mp = grp.m_part[w2][lane], lp = grp.l_part[w2][lane];
+            l_tot += (mp == -INFINITY) ? 0.f : lp * ex2_approx((mp - m_fin) * c);
+          }
+        }
+        const float inv = ((l_tot == 0.f || l_tot != l_tot) ? 1.f : 1.f / l_tot) * args.o_scale;
+        // Each warp of the pair writes half of the head dimension.
+        __half* o_row = args.o + (static_cast<size_t>(bh) * seqlen + q_row) * D + h * (D / 2);
+#pragma unroll
+        for (int q = 0; q < D / 64; ++q) {
           uint32_t orow[32];
-          tmem_ld_32x32b_x32(t_o + 32 * q, orow);
+          tmem_ld_32x32b_x32(t_o + h * (D / 2) + 32 * q, orow);
           tmem_wait_ld();
           if (q_row < seqlen) {
 #pragma unroll

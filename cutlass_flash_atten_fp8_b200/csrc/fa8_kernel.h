@@ -17,9 +17,6 @@ struct KernelArgs {
   float o_scale;                  // multiplies O/l (1 = reference behaviour)
   int* status;                    // optional device word; non-zero after a bounded wait expired
   unsigned long long timeout_ns;  // bound of every mbarrier wait
-#ifdef FA8_TIMING
-  long long* dbg;                 // debug builds only: per-warp phase cycle counters
-#endif
 };
 
 // Launches the forward kernel for head_dim in {64,128}; grid = (n_pairs, bh).
