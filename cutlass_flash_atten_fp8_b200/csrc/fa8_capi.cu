@@ -108,7 +108,6 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   int sup = fa8_supported(p->seqlen, p->head_dim, p->v_layout);
   if (sup != FA8_OK) return sup;
   const int64_t bh = static_cast<int64_t>(p->batch) * p->heads;
-  if (bh > 65535) return FA8_ERR_UNSUPPORTED;   // grid.y
 
   const uint64_t S = static_cast<uint64_t>(p->seqlen), D = static_cast<uint64_t>(p->head_dim);
   const CUtensorMapSwizzle sw_qk = (p->head_dim == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
@@ -125,9 +124,12 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   args.o_scale = p->o_scale;
   args.status = p->status_word;
   args.timeout_ns = 2000000000ull;
-  const int n_pairs = (p->seqlen + 255) / 256;
-  cudaError_t e = fa8::launch_fwd(p->head_dim, p->is_causal != 0, tq, tk, tv, args, n_pairs,
-                                  static_cast<int>(bh), static_cast<cudaStream_t>(cuda_stream));
+  args.n_pairs = (p->seqlen + 255) / 256;
+  const int64_t per_slice = p->is_causal ? (args.n_pairs + 1) / 2 : args.n_pairs;
+  if (bh * per_slice > 0x7fffffff) return FA8_ERR_UNSUPPORTED;
+  args.n_units = static_cast<int>(bh * per_slice);
+  cudaError_t e = fa8::launch_fwd(p->head_dim, p->is_causal != 0, tq, tk, tv, args,
+                                  static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess) {
     set_detail("kernel launch", cudaGetErrorString(e));
     return FA8_ERR_CUDA;

@@ -5,18 +5,21 @@
 // (csrc/kernel_traits.h:33-130), FP8 mma.sync atoms (csrc/mma_sm89.hpp,
 // csrc/mma_traits_sm89.hpp) and the C->A register shuffle (csrc/reg2reg.h).
 //
-// One CTA owns two 128-row query tiles of one (batch, head) slice and walks the
+// The grid is persistent (one CTA per SM); a CTA takes one work item after the other,
+// each being two 128-row query tiles of one (batch, head) slice, and walks the
 // key/value sequence; K and V^T arrive as 128-position tiles, the arithmetic runs
 // on 64-position sub-blocks so that each query tile has TWO score buffers in
 // tensor memory and its next S = Q K^T is computed while the softmax of the
 // current sub-block is still running:
 //
-//   warp 17     TMA producer: Q tiles once, then K_j / V_j tiles into a ring of
-//               shared-memory slots, each guarded by a full/empty mbarrier pair.
-//   warp 16     MMA issuer (one elected lane): S_i[sb&1] = Q_i K_sb^T (M128 N64)
-//               and O_i += P_i(sb) V_sb (M128 N=head_dim) as tcgen05.mma
-//               kind::f8f6f4 with fp32 accumulators in tensor memory; completion
-//               is signalled with tcgen05.commit on mbarriers.
+//   warp 18     TMA producer: Q tiles (double-buffered across work items), then K_j /
+//               V_j tiles into a ring of shared-memory slots, each guarded by a
+//               full/empty mbarrier pair.
+//   warps 16,17 MMA issuers, one per query tile (one elected lane each):
+//               S_i[sb&1] = Q_i K_sb^T (M128 N64) and O_i += P_i(sb) V_sb
+//               (M128 N=head_dim) as tcgen05.mma kind::f8f6f4 with fp32 accumulators
+//               in tensor memory; completion is signalled with tcgen05.commit on
+//               mbarriers.
 //   warps 0-7   online softmax for query tile 0, warps 8-15 for tile 1.  A TMEM lane
 //               is a query row (tcgen05.ld 32x32b: one row per thread, no shuffles).
 //               Warps w and w+4 of a tile own the same 32 rows: the first takes the
@@ -59,9 +62,9 @@ namespace {
 constexpr int kTileM = 128;        // query rows per tile = TMEM lanes
 constexpr int kBlockN = 128;       // key/value positions per TMA tile
 constexpr int kSubN = 64;          // key/value positions per MMA / softmax sub-block
-constexpr int kMmaWarp = 16;
-constexpr int kLoadWarp = 17;
-constexpr int kThreads = 576;
+constexpr int kMmaWarp0 = 16;      // warps 16 and 17: MMA issuers of query tile 0 and 1
+constexpr int kLoadWarp = 18;
+constexpr int kThreads = 608;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemO = 256;   // first O column; S_0 at 0, S_1 at 128
 
@@ -70,12 +73,13 @@ struct Cfg {
   static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
   static constexpr int kTileBytes = 128 * D;           // Q, K and V^T tiles alike
   static constexpr int kSlots = (D == 128) ? 8 : 16;   // ring slots, one K or V tile each
-  static constexpr int kQBytes = 2 * kTileBytes;
+  static constexpr int kQBytes = 4 * kTileBytes;           // two tiles x two stages (work items)
   static constexpr int kRingBytes = kSlots * kTileBytes;
   static constexpr int kBarOffset = kQBytes + kRingBytes;
   // row-group scratch shared by the two warps of a 32-row group, see RowGroupShared
-  static constexpr int kGroupBytes = 8 * 672;
-  static constexpr int kNumBars = 2 /*q_full*/ + 2 * kSlots + 4 /*s_full*/ + 4 /*p_full*/ + 2 /*o_done*/ + 2 /*o_final*/ + 1 /*drain*/;
+  static constexpr int kGroupBytes = 8 * 1184;
+  static constexpr int kNumBars = 4 /*q_full*/ + 4 /*q_empty*/ + 2 * kSlots + 4 /*s_full*/ + 4 /*p_full*/ +
+                                  2 /*o_done*/ + 2 /*o_final*/ + 2 /*o_free*/ + 2 /*drain*/;
   static constexpr int kSmemBytes = kBarOffset + kNumBars * 8 + 16 /*tmem ptr, abort*/ + kGroupBytes + 1024 /*align*/;
   // Q and K rows are D bytes long: one 128-byte swizzle row for D=128, a 64-byte one for D=64.
   static constexpr uint32_t kQKLayout = (D == 128) ? 2u : 4u;   // UMMA SWIZZLE_128B / SWIZZLE_64B
@@ -124,6 +128,9 @@ __device__ __forceinline__ bool wait_bounded(const WaitCtx& w, uint32_t bar, uin
 // ------------------------------------------------------------ softmax passes
 // Which of the 16 element pairs of a 32-column chunk take their exponential on the FMA
 // pipe instead of the special-function unit (bit p = pair p).
+#ifndef FA8_MMA_IDLE_SLEEP_NS
+#define FA8_MMA_IDLE_SLEEP_NS 0   // pause of the MMA lane between two fruitless polls of the P barriers
+#endif
 #ifndef FA8_POLY_PAIR_MASK
 #define FA8_POLY_PAIR_MASK 0x1111
 #endif
@@ -250,17 +257,67 @@ __device__ __noinline__ void rescale_o_columns(uint32_t t_o, int chunks, float a
   tmem_wait_st();
 }
 
-// What the two warps of a 32-row group share (672 bytes per group): the row maxima the
+// What the two warps of a 32-row group share (1184 bytes per group): the row maxima the
 // exponentials are taken against, a version counter bumped whenever they are raised,
 // and each warp's final (row sum, maximum it refers to) for the epilogue.
 struct RowGroupShared {
   volatile float m[32];
   volatile uint32_t version;
   uint32_t pad[7];
-  volatile float l_part[2][32];
-  volatile float m_part[2][32];
+  volatile float l_part[2][2][32];   // [work item parity][warp of the pair][row]
+  volatile float m_part[2][2][32];
 };
-static_assert(sizeof(RowGroupShared) == 672, "RowGroupShared layout");
+static_assert(sizeof(RowGroupShared) == 1184, "RowGroupShared layout");
+
+// One work item: two 128-row query tiles of one (batch, head) slice.
+struct Item {
+  int bh;          // slice
+  int row0;        // first query row of tile 0
+  int nsb_t[2];    // 64-key sub-blocks each tile visits (0 = the tile lies past the end)
+  int nsb;         // max of the two
+  int nb;          // 128-key K/V tiles to load
+};
+
+// Work decomposition of the persistent grid.  CTA c takes units c, c + gridDim.x, ...
+// Non-causal: a unit is one tile pair, slice-major (the CTAs running side by side work on
+// the same few slices, whose K and V stay in L2).  Causal: the cost of a pair grows with
+// its position, so a unit folds pair f with pair n-1-f of the same slice (heavy one
+// first) and every unit costs the same.
+template <bool kCausal>
+__device__ __forceinline__ bool get_item(const KernelArgs& a, int unit, int k, Item& it) {
+  const int n_pairs = a.n_pairs;
+  int pair;
+  if (!kCausal) {
+    if (k > 0) return false;
+    it.bh = unit / n_pairs;
+    pair = unit - it.bh * n_pairs;
+  } else {
+    const int n_fold = (n_pairs + 1) >> 1;
+    it.bh = unit / n_fold;
+    const int f = unit - it.bh * n_fold;
+    const int hi = n_pairs - 1 - f;
+    if (k == 0) {
+      pair = hi;
+    } else {
+      if (hi == f) return false;
+      pair = f;
+    }
+  }
+  it.row0 = pair * 2 * kTileM;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r0 = it.row0 + i * kTileM;
+    int n = 0;
+    if (r0 < a.seqlen) {
+      const int col_end = kCausal ? min(r0 + kTileM, a.seqlen) : a.seqlen;   // one past the last visible key
+      n = (col_end + kSubN - 1) / kSubN;
+    }
+    it.nsb_t[i] = n;
+  }
+  it.nsb = max(it.nsb_t[0], it.nsb_t[1]);
+  it.nb = (it.nsb + 1) >> 1;
+  return true;
+}
 
 }  // namespace
 
@@ -269,26 +326,36 @@ __global__ void __launch_bounds__(kThreads, 1)
 fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const KernelArgs args) {
   using C = Cfg<D>;
+  constexpr int kItemsPerUnit = kCausal ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
+  // Q tiles are double-buffered across work items: s_q + (2*stage + tile) * kTileBytes.
   const uint32_t s_q = smem_base;
   const uint32_t s_ring = smem_base + C::kQBytes;
   const uint32_t s_bar = smem_base + C::kBarOffset;
-  auto bar_q_full = [&](int i) { return s_bar + 8u * i; };
-  auto bar_kv_full = [&](int s) { return s_bar + 8u * (2 + s); };
-  auto bar_kv_empty = [&](int s) { return s_bar + 8u * (2 + C::kSlots + s); };
-  auto bar_s_full = [&](int i, int h) { return s_bar + 8u * (2 + 2 * C::kSlots + 2 * i + h); };
-  // One P barrier per S buffer: a softmax warp may run one sub-block ahead of its
-  // siblings (the next S is already there), never two.
-  auto bar_p_full = [&](int i, int h) { return s_bar + 8u * (6 + 2 * C::kSlots + 2 * i + h); };
-  auto bar_o_done = [&](int i) { return s_bar + 8u * (10 + 2 * C::kSlots + i); };
-  // Completes once, after the last PV of tile i.  (The epilogue cannot use o_done: a warp
-  // that ran ahead of its siblings may get there two phases early, which a parity wait
-  // cannot tell from "done".)
-  auto bar_o_final = [&](int i) { return s_bar + 8u * (12 + 2 * C::kSlots + i); };
-  const uint32_t bar_drain = s_bar + 8u * (14 + 2 * C::kSlots);
+  int bar_idx = 0;
+  auto take = [&](int n) { const uint32_t a = s_bar + 8u * bar_idx; bar_idx += n; return a; };
+  const uint32_t b_q_full = take(4), b_q_empty = take(4);            // [tile][stage]
+  const uint32_t b_kv_full = take(C::kSlots), b_kv_empty = take(C::kSlots);
+  const uint32_t b_s_full = take(4), b_p_full = take(4);             // [tile][S buffer]
+  const uint32_t b_o_done = take(2), b_o_final = take(2), b_o_free = take(2);
+  const uint32_t bar_drain = take(2);
+  auto bar_q_full = [&](int i, int st) { return b_q_full + 8u * (2 * i + st); };
+  auto bar_q_empty = [&](int i, int st) { return b_q_empty + 8u * (2 * i + st); };
+  auto bar_kv_full = [&](int s) { return b_kv_full + 8u * s; };
+  auto bar_kv_empty = [&](int s) { return b_kv_empty + 8u * s; };
+  auto bar_s_full = [&](int i, int h) { return b_s_full + 8u * (2 * i + h); };
+  // One P barrier per S buffer (= per warp of a row-group pair).
+  auto bar_p_full = [&](int i, int h) { return b_p_full + 8u * (2 * i + h); };
+  // o_done[i]: one phase per PV of tile i.  o_final[i]: one phase per work item, after the
+  // tile's last PV (the epilogue cannot use o_done: warps get there at different distances
+  // from the end, which a parity wait cannot tell apart).  o_free[i]: one phase per work
+  // item, when all eight warps of the tile have read O out of tensor memory.
+  auto bar_o_done = [&](int i) { return b_o_done + 8u * i; };
+  auto bar_o_final = [&](int i) { return b_o_final + 8u * i; };
+  auto bar_o_free = [&](int i) { return b_o_free + 8u * i; };
   volatile uint32_t* tmem_ptr_slot =
       reinterpret_cast<volatile uint32_t*>(smem_gen + C::kBarOffset + C::kNumBars * 8);
   volatile int* abort_flag =
@@ -299,51 +366,35 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int seqlen = args.seqlen;
-  // Causal work grows with the query position: schedule the long tiles first.
-  const int pair = kCausal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
-  const int bh = blockIdx.y;
-  const int row0 = pair * 2 * kTileM;                 // first query row of tile 0
-  // Number of 64-position sub-blocks each tile visits (0 = the tile lies past the end).
-  int nsb_t[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int r0 = row0 + i * kTileM;
-    int n = 0;
-    if (r0 < seqlen) {
-      const int col_end = kCausal ? min(r0 + kTileM, seqlen) : seqlen;   // one past the last visible key
-      n = (col_end + kSubN - 1) / kSubN;
-    }
-    nsb_t[i] = n;
-  }
-  const int nsb = max(nsb_t[0], nsb_t[1]);
-  const int nb = (nsb + 1) / 2;                       // K/V tiles to load
-
   const WaitCtx wctx{abort_flag, args.status, args.timeout_ns};
 
   if (threadIdx.x == 0) {
     // A status word that is already non-zero (an earlier CTA of this launch gave up, or the
     // caller did not clear it) makes the CTA return at once: a failed launch then costs one
-    // wait limit, not one per wave of CTAs.
+    // wait limit, not one per CTA.
     *abort_flag = (args.status != nullptr && *reinterpret_cast<volatile int*>(args.status) != 0) ? 2 : 0;
-    for (int i = 0; i < 2; ++i) mbar_init(bar_q_full(i), 1);
+    for (int x = 0; x < 4; ++x) {
+      mbar_init(b_q_full + 8u * x, 1);
+      mbar_init(b_q_empty + 8u * x, 1);
+      mbar_init(b_s_full + 8u * x, 1);
+      mbar_init(b_p_full + 8u * x, 4);     // one arrive per softmax warp of the (tile, buffer)
+    }
     for (int s = 0; s < C::kSlots; ++s) {
       mbar_init(bar_kv_full(s), 1);
-      mbar_init(bar_kv_empty(s), 1);
+      mbar_init(bar_kv_empty(s), 2);       // both MMA issuers hand a slot back
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar_s_full(i, 0), 1);
-      mbar_init(bar_s_full(i, 1), 1);
-      mbar_init(bar_p_full(i, 0), 4);   // one arrive per softmax warp
-      mbar_init(bar_p_full(i, 1), 4);
       mbar_init(bar_o_done(i), 1);
       mbar_init(bar_o_final(i), 1);
+      mbar_init(bar_o_free(i), 8);         // one arrive per softmax warp of the tile
     }
     mbar_init(bar_drain, 1);
+    mbar_init(bar_drain + 8u, 1);
     for (int g = 0; g < 8; ++g) groups[g].version = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
   }
-  if (warp == kMmaWarp) {
+  if (warp == kMmaWarp0) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
     tmem_relinquish();
   }
@@ -363,8 +414,9 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
       bool ok = true;
-      int it = 0;   // K_j is load 2j, V_j is load 2j+1
-      auto load_kv = [&](const CUtensorMap* tm, int c0, int c1) {
+      int it = 0;                 // K/V loads issued so far; slot = it % kSlots
+      int qn[2] = {0, 0};         // Q loads issued so far per tile; stage = qn & 1
+      auto load_kv = [&](const CUtensorMap* tm, int c0, int c1, int bh) {
         const int slot = it % C::kSlots;
         const uint32_t round = static_cast<uint32_t>(it / C::kSlots);
         if (ok) ok = wait_bounded(wctx, bar_kv_empty(slot), (round & 1u) ^ 1u, 0x100 + slot);
@@ -374,22 +426,34 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           ++it;
         }
       };
-      load_kv(&tm_k, 0, 0);
+      for (int unit = blockIdx.x; unit < args.n_units && ok; unit += gridDim.x) {
+        for (int k = 0; k < kItemsPerUnit && ok; ++k) {
+          Item w;
+          if (!get_item<kCausal>(args, unit, k, w)) continue;
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        if (nsb_t[i] > 0) {
-          mbar_arrive_expect_tx(bar_q_full(i), C::kTileBytes);
-          tma_load_3d(s_q + i * C::kTileBytes, &tm_q, bar_q_full(i), 0, row0 + i * kTileM, bh);
+          for (int i = 0; i < 2; ++i) {
+            if (w.nsb_t[i] > 0 && ok) {
+              const int st = qn[i] & 1;
+              const uint32_t round = static_cast<uint32_t>(qn[i] >> 1);
+              ok = wait_bounded(wctx, bar_q_empty(i, st), (round & 1u) ^ 1u, 0x180 + i);
+              if (ok) {
+                mbar_arrive_expect_tx(bar_q_full(i, st), C::kTileBytes);
+                tma_load_3d(s_q + (2 * st + i) * C::kTileBytes, &tm_q, bar_q_full(i, st), 0,
+                            w.row0 + i * kTileM, w.bh);
+                ++qn[i];
+              }
+            }
+          }
+          for (int j = 0; j < w.nb && ok; ++j) {
+            load_kv(&tm_k, 0, j * kBlockN, w.bh);
+            load_kv(&tm_v, j * kBlockN, 0, w.bh);
+          }
         }
       }
-      load_kv(&tm_v, 0, 0);
-      for (int j = 1; j < nb && ok; ++j) {
-        load_kv(&tm_k, 0, j * kBlockN);
-        load_kv(&tm_v, j * kBlockN, 0);
-      }
       if (!ok) {
-        // Abort: let this CTA's copies that are still in flight land before the
-        // shared memory is given back.  Loads [it - kSlots, it) may be pending.
+        // Abort: let this CTA's copies that are still in flight land before the shared
+        // memory is given back.  K/V loads [it - kSlots, it) and the last two Q loads of
+        // each tile may be pending.
         for (int p = max(0, it - C::kSlots); p < it; ++p) {
           const int slot = p % C::kSlots;
           const uint32_t round = static_cast<uint32_t>(p / C::kSlots);
@@ -400,9 +464,9 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-          if (nsb_t[i] > 0) {
+          for (int p = max(0, qn[i] - 2); p < qn[i]; ++p) {
             const uint64_t t0 = global_timer_ns();
-            while (!mbar_try_wait(bar_q_full(i), 0)) {
+            while (!mbar_try_wait(bar_q_full(i, p & 1), static_cast<uint32_t>(p >> 1) & 1u)) {
               if (global_timer_ns() - t0 > 20000000ull) break;
             }
           }
@@ -410,93 +474,123 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     }
     __syncwarp();
-  } else if (warp == kMmaWarp) {
-    // -------------------------------------------------------------- MMA issuer
+  } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+    // ------------------------------------------------- MMA issuers, one per query tile
+    // Each issues, for its tile i, S_i[sb&1] = Q_i K_sb^T and O_i += P_i(sb) V_sb.  The two
+    // never wait for one another; a K/V ring slot goes back to the producer when both have
+    // committed it (kv_empty counts two arrivals).
     if (elect_one()) {
+      const int i = warp - kMmaWarp0;
       constexpr uint32_t kIdescQK = umma_idesc(kTileM, kSubN);
       constexpr uint32_t kIdescPV = umma_idesc(kTileM, D);
+      constexpr uint32_t kSlotMask = C::kSlots - 1;
+      static_assert((C::kSlots & (C::kSlots - 1)) == 0, "ring size must be a power of two");
+      constexpr int kSlotShift = (C::kSlots == 8) ? 3 : 4;
       bool ok = true;
-      auto slot_of = [&](int load) { return load % C::kSlots; };
-      auto parity_of = [&](int load) { return static_cast<uint32_t>(load / C::kSlots) & 1u; };
-      auto wait_load = [&](int load) {
-        if (ok) ok = wait_bounded(wctx, bar_kv_full(slot_of(load)), parity_of(load), 0x200 + slot_of(load));
-      };
+      uint32_t kv_base = 0;            // index of the current item's first K/V load (K_0)
+      uint32_t qn = 0;                 // work items of this tile so far
+      uint32_t p_cnt0 = 0, p_cnt1 = 0; // P phases consumed per S buffer
+      const uint32_t t_s = tmem_base + i * kBlockN;
+      const uint32_t t_o = tmem_base + kTmemO + i * D;
+      // Descriptors differ only in the 14-bit start-address field (units of 16 bytes).
+      const uint64_t dq_base = umma_desc(s_q + i * C::kTileBytes, C::kQKSbo, C::kQKLayout);
+      const uint64_t dk_base = umma_desc(s_ring, C::kQKSbo, C::kQKLayout);
+      const uint64_t dv_base = umma_desc(s_ring, 1024u, 2u);
+      auto slot_of = [&](uint32_t load) { return load & kSlotMask; };
+      auto parity_of = [&](uint32_t load) { return (load >> kSlotShift) & 1u; };
       // S_i[h] = Q_i K_sb^T for sub-block sb = 2j+h: rows 64h..64h+63 of tile K_j;
       // D/32 steps of K=32 bytes along the swizzled rows.
-      auto issue_qk = [&](int i, int h, int load) {
-        const uint64_t dq = umma_desc(s_q + i * C::kTileBytes, C::kQKSbo, C::kQKLayout);
-        const uint64_t dk = umma_desc(s_ring + slot_of(load) * C::kTileBytes + h * kSubN * D,
-                                      C::kQKSbo, C::kQKLayout);
+      auto issue_qk = [&](uint32_t st, int h, uint32_t load) {
+        const uint64_t dq = dq_base + st * (2 * C::kTileBytes / 16);
+        const uint64_t dk = dk_base + (slot_of(load) * C::kTileBytes + h * kSubN * D) / 16;
 #pragma unroll
         for (int k = 0; k < D / 32; ++k)
-          mma_f8_ss(tmem_base + i * kBlockN + h * kSubN, dq + 2u * k, dk + 2u * k, kIdescQK, k > 0);
+          mma_f8_ss(t_s + h * kSubN, dq + 2u * k, dk + 2u * k, kIdescQK, k > 0);
       };
       // O_i (+)= P_i(sb) V_sb: P is 128 rows x 64 e4m3 = 16 TMEM columns over S_i[h];
       // the V^T tile is D rows of 128 key positions (K-major, 128-byte swizzle), of which
       // sub-block h covers bytes 64h..64h+63 of every row = K-steps 2h and 2h+1.
-      auto issue_pv = [&](int i, int h, int load, bool acc) {
-        const uint64_t dv = umma_desc(s_ring + slot_of(load) * C::kTileBytes, 1024u, 2u);
+      auto issue_pv = [&](int h, uint32_t load, bool acc) {
+        const uint64_t dv = dv_base + (slot_of(load) * C::kTileBytes) / 16 + 4u * h;
 #pragma unroll
         for (int k = 0; k < kSubN / 32; ++k)
-          mma_f8_ts(tmem_base + kTmemO + i * D, tmem_base + i * kBlockN + h * kSubN + 8u * k,
-                    dv + 2u * (2 * h + k), kIdescPV, (acc || k > 0) ? 1u : 0u);
+          mma_f8_ts(t_o, t_s + h * kSubN + 8u * k, dv + 2u * k, kIdescPV, (acc || k > 0) ? 1u : 0u);
       };
 
-      wait_load(0);
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        if (nsb_t[i] > 0) {
-          if (ok) ok = wait_bounded(wctx, bar_q_full(i), 0, 0x300 + i);
-          if (ok) {
-            tc_fence_after();
-            issue_qk(i, 0, 0);
-            tc_commit(bar_s_full(i, 0));
-          }
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        if (nsb_t[i] > 1 && ok) {
-          issue_qk(i, 1, 0);
-          tc_commit(bar_s_full(i, 1));
-        }
-      }
-      if (ok) tc_commit(bar_kv_empty(slot_of(0)));
-
-      for (int sb = 0; sb < nsb && ok; ++sb) {
-        const int j = sb >> 1, h = sb & 1;
-        const int ld_v = 2 * j + 1, ld_kn = 2 * j + 2;      // V_j and K_{j+1}
-        const bool kn_loaded = (2 * j + 2 < nsb);
-        if (h == 0) {
-          wait_load(ld_v);
-          if (kn_loaded) wait_load(ld_kn);
-        }
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          if (sb < nsb_t[i]) {
-            if (ok) ok = wait_bounded(wctx, bar_p_full(i, h), static_cast<uint32_t>(sb >> 1) & 1u, 0x400 + i);
+      for (int unit = blockIdx.x; unit < args.n_units && ok; unit += gridDim.x) {
+        for (int kk = 0; kk < kItemsPerUnit && ok; ++kk) {
+          Item w;
+          if (!get_item<kCausal>(args, unit, kk, w)) continue;
+          const int nsb = (i == 0) ? w.nsb_t[0] : w.nsb_t[1];
+          const uint32_t n_loads = 2u * static_cast<uint32_t>(w.nb);
+          // The item's loads are K_0, V_0, K_1, V_1, ... = kv_base + 0, 1, 2, ...  This thread
+          // waits for each of them once, in order, and hands each back once, in order
+          // (`released` of them so far), whether or not its tile reads it.
+          uint32_t waited = 0, released = 0;
+          auto wait_upto = [&](uint32_t idx) {
+            while (waited <= idx && ok) {
+              const uint32_t load = kv_base + waited;
+              ok = wait_bounded(wctx, bar_kv_full(slot_of(load)), parity_of(load), 0x200 + slot_of(load));
+              ++waited;
+            }
+          };
+          auto release_upto = [&](uint32_t idx) {      // hands back loads released..idx
+            while (released <= idx && ok) {
+              wait_upto(released);                     // one at a time: a later load may need this slot
+              if (ok) tc_commit(bar_kv_empty(slot_of(kv_base + released)));
+              ++released;
+            }
+          };
+          if (nsb > 0) {
+            const uint32_t st = qn & 1u;
+            // Prologue: the first two S need no P.
+            wait_upto(0);
+            if (ok) ok = wait_bounded(wctx, bar_q_full(i, st), (qn >> 1) & 1u, 0x300 + i);
             if (ok) {
               tc_fence_after();
-              issue_pv(i, h, ld_v, sb > 0);
-              tc_commit(bar_o_done(i));                    // phase sb: PV_i(0..sb) complete
-              if (sb == nsb_t[i] - 1) tc_commit(bar_o_final(i));
-              if (sb + 2 < nsb_t[i]) {
-                issue_qk(i, h, ld_kn);
-                tc_commit(bar_s_full(i, h));               // S_i[h] now holds sub-block sb+2
+              issue_qk(st, 0, kv_base);
+              tc_commit(bar_s_full(i, 0));
+              if (nsb > 1) {
+                issue_qk(st, 1, kv_base);
+                tc_commit(bar_s_full(i, 1));
               }
+              if (nsb <= 2) tc_commit(bar_q_empty(i, st));
+              release_upto(0);                                      // K_0
             }
+            // Step sb: PV(sb), then QK(sb+2) into the buffer PV just freed.
+            for (int sb = 0; sb < nsb && ok; ++sb) {
+              const int h = sb & 1;
+              const uint32_t j2 = static_cast<uint32_t>(sb) & ~1u;          // 2j
+              wait_upto(sb + 2 < nsb ? j2 + 2 : j2 + 1);                     // V_j (and K_{j+1})
+              if (ok) ok = wait_bounded(wctx, bar_p_full(i, h), (h ? p_cnt1 : p_cnt0) & 1u, 0x400 + i);
+              if (sb == 0 && qn > 0 && ok)                                 // O_i of the previous item read out?
+                ok = wait_bounded(wctx, bar_o_free(i), (qn - 1) & 1u, 0x480 + i);
+              if (!ok) break;
+              tc_fence_after();
+              issue_pv(h, kv_base + j2 + 1, sb > 0);
+              tc_commit(bar_o_done(i));
+              if (sb == nsb - 1) tc_commit(bar_o_final(i));
+              if (sb + 2 < nsb) {
+                issue_qk(st, h, kv_base + j2 + 2);
+                tc_commit(bar_s_full(i, h));                                 // S_i[h] now holds sub-block sb+2
+                if (sb + 2 == nsb - 1) tc_commit(bar_q_empty(i, st));
+              }
+              if (h) ++p_cnt1; else ++p_cnt0;
+              // V_j was last read by PV(2j+1), K_{j+1} by QK(2j+3), both issued in step 2j+1.
+              if (h == 1) release_upto(min(j2 + 2, n_loads - 1));
+            }
+            ++qn;
           }
-        }
-        if (ok && (h == 1 || sb == nsb - 1)) {
-          tc_commit(bar_kv_empty(slot_of(ld_v)));
-          if (h == 1 && kn_loaded) tc_commit(bar_kv_empty(slot_of(ld_kn)));
+          if (ok) release_upto(n_loads - 1);                          // whatever this tile did not read
+          kv_base += n_loads;
         }
       }
       if (!ok) {
         // Abort: wait (bounded) for the MMAs already issued before TMEM is freed.
-        tc_commit(bar_drain);
+        const uint32_t bd = bar_drain + 8u * i;
+        tc_commit(bd);
         const uint64_t t0 = global_timer_ns();
-        while (!mbar_try_wait(bar_drain, 0)) {
+        while (!mbar_try_wait(bd, 0)) {
           if (global_timer_ns() - t0 > 20000000ull) break;
         }
       }
@@ -511,126 +605,142 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t t_sb = tmem_base + lane_sel + i * kBlockN + h * kSubN;   // my S buffer
     const uint32_t t_o = tmem_base + lane_sel + kTmemO + i * D;
-    const int q_row = row0 + i * kTileM + row;         // global query row, may be >= seqlen
-    const int tile_nsb = nsb_t[i];
-    const int col_lim = kCausal ? min(seqlen, q_row + 1) : seqlen;   // keys this row may see
     const float c = args.scale_log2;
     RowGroupShared& grp = groups[i * 4 + quarter];
-    // m is the row maximum the exponentials are taken against, shared by the two warps of
-    // the row group through grp.m / grp.version: exact after sub-block 0, then raised only
-    // by the exact path below.  l is this warp's share of the row sum, kept relative to m.
-    // O and both shares are sums against the same m, so O/l does not depend on when m is
-    // raised.
-    float m = -INFINITY, l = 0.f;
-    uint32_t version = 0;
+    // Running phase counts of the barriers this warp waits on.
+    uint32_t own_cnt = 0;        // sub-blocks taken from my S buffer: s_full[i][h] phases consumed
+    uint32_t peer_cnt = 0;       // partner's sub-blocks before the current item: p_full[i][h^1] base
+    uint32_t pv_cnt = 0;         // PVs of this tile before the current item: o_done[i] base
+    uint32_t items = 0;          // work items of this tile so far: o_final[i] phase, l_part buffer
+    uint32_t version = 0;        // last value of grp.version this warp has seen
     bool ok = true;
 
-    // Brings m (and l with it) up to date with the partner's latest raise.
-    auto adopt = [&]() -> bool {
-      const uint32_t v = grp.version;
-      if (v == version) return false;
-      __threadfence_block();
-      const float m_new = grp.m[lane];
-      if (m != -INFINITY) l *= ex2_approx((m - m_new) * c);
-      m = m_new;
-      version = v;
-      return true;
-    };
+    for (int unit = blockIdx.x; unit < args.n_units && ok; unit += gridDim.x) {
+      for (int kk = 0; kk < kItemsPerUnit && ok; ++kk) {
+        Item w;
+        if (!get_item<kCausal>(args, unit, kk, w)) continue;
+        const int tile_nsb = w.nsb_t[i];
+        if (tile_nsb == 0) continue;
+        const int q_row = w.row0 + i * kTileM + row;       // global query row, may be >= seqlen
+        const int col_lim = kCausal ? min(seqlen, q_row + 1) : seqlen;   // keys this row may see
+        const uint32_t ib = items & 1u;
+        // m is the row maximum the exponentials are taken against, shared by the two warps
+        // of the row group through grp.m / grp.version: exact after sub-block 0, then raised
+        // only by the exact path below.  l is this warp's share of the row sum, kept relative
+        // to m.  O and both shares are sums against the same m, so O/l does not depend on
+        // when m is raised.
+        float m = -INFINITY, l = 0.f;
+        bool have_m = false;
 
-    for (int sb = h; sb < tile_nsb; sb += 2) {
-      const uint32_t ph = static_cast<uint32_t>(sb >> 1) & 1u;
-      ok = wait_bounded(wctx, bar_s_full(i, h), ph, 0x500 + i);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const int lim = col_lim - sb * kSubN;            // sub-block-local first masked column
+        for (int sb = h; sb < tile_nsb; sb += 2) {
+          bool ok_s = wait_bounded(wctx, bar_s_full(i, h), own_cnt & 1u, 0x500 + i);
+          tc_fence_after();
+          const int lim = col_lim - sb * kSubN;            // sub-block-local first masked column
 
-      uint32_t pk[16];
-      float bsum = 0.f;
-      const bool have_m = (version != 0);              // warp-uniform
-      if (have_m) {
-        // Fast path: one pass, exponentials against the maximum known so far.
-        bsum = softmax_pass<true>(t_sb, lim, c, -m * c, pk);
-      }
-      // P(sb) may be handed over only after the partner has handed over P(sb-1): from then
-      // on nobody else can raise the maximum before PV(sb) is issued.
-      if (sb > 0) {
-        ok = wait_bounded(wctx, bar_p_full(i, h ^ 1), static_cast<uint32_t>((sb - 1) >> 1) & 1u, 0x800 + i);
+          uint32_t pk[16];
+          float bsum = 0.f;
+          // Fast path: one pass, exponentials against the maximum known so far.
+          if (have_m) bsum = softmax_pass<true>(t_sb, lim, c, -m * c, pk);
+          // P(sb) may be handed over only after the partner has handed over P(sb-1): from
+          // then on nobody else can raise the maximum before PV(sb) is issued.
+          if (sb > 0)
+            ok_s = wait_bounded(wctx, bar_p_full(i, h ^ 1), (peer_cnt + static_cast<uint32_t>((sb - 1) >> 1)) & 1u,
+                                0x800 + i) && ok_s;
+          // One vote settles the common case: waits fine, maximum unchanged, no overflow.
+          // Some P above kLazyLimit implies a sum above it (all P >= 0); a false alarm only
+          // costs the exact path.  Decided for the warp's 32 rows as a whole.
+          const uint32_t v = grp.version;
+          const bool calm = ok_s && have_m && (v == version) && (bsum <= kLazyLimit);
+          if (!__all_sync(0xffffffffu, calm)) {
+            ok = __all_sync(0xffffffffu, ok_s);
+            if (!ok) break;
+            bool exact = (sb == 0);
+            if (!exact) {
+              if (v != version || !have_m) {
+                // The partner raised the maximum (or this is my first sub-block of the item).
+                __threadfence_block();
+                const float m_new = grp.m[lane];
+                if (have_m) l *= ex2_approx((m - m_new) * c);
+                m = m_new;
+                version = v;
+                have_m = true;
+                bsum = softmax_pass<false>(t_sb, lim, c, -m * c, pk);
+              }
+              exact = __any_sync(0xffffffffu, !(bsum <= kLazyLimit));
+            }
+            if (exact) {
+              // Exact path (first sub-block, or the maximum is too low for some row of this
+              // warp): true row maximum, rescale l and O, publish, redo the exponentials.
+              const float m_new = fmaxf(m, row_max(t_sb, lim));
+              if (sb > 0) {
+                // O_i must be quiescent: PV_i(sb-1) complete; PV_i(sb) waits for this warp.
+                ok = wait_bounded(wctx, bar_o_done(i), (pv_cnt + static_cast<uint32_t>(sb - 1)) & 1u, 0x700 + i);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                float alpha = ex2_approx((m - m_new) * c);
+                if (m == -INFINITY) alpha = 1.f;
+                l *= alpha;
+                rescale_o_columns(t_o, D / 32, alpha);
+              }
+              m = m_new;
+              have_m = true;
+              grp.m[lane] = m_new;
+              __threadfence_block();
+              __syncwarp();
+              version = grp.version + 1;
+              __syncwarp();
+              if (lane == 0) grp.version = version;
+              bsum = softmax_pass<false>(t_sb, lim, c, (m == -INFINITY) ? 0.f : -m * c, pk);
+            }
+          }
+          l += bsum;
+          if (sb + 2 >= tile_nsb) {                        // my last sub-block: leave my share for the epilogue
+            grp.l_part[ib][h][lane] = l;
+            grp.m_part[ib][h][lane] = m;
+            __threadfence_block();
+          }
+          tmem_st_32x32b_x16(t_sb, pk);
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_p_full(i, h));
+          ++own_cnt;
+        }
+        if (!ok) break;
+        peer_cnt += static_cast<uint32_t>((tile_nsb + h) >> 1);     // partner's sub-blocks in this item
+        pv_cnt += static_cast<uint32_t>(tile_nsb);
+
+        // Epilogue: O_i / l -> fp16 -> global; each warp of the pair writes half the head dim.
+        ok = wait_bounded(wctx, bar_o_final(i), items & 1u, 0x600 + i);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-      }
-      bool redo = adopt() || !have_m;                  // warp-uniform: version is per group
-      redo = __any_sync(0xffffffffu, redo);
-      // Some P above kLazyLimit implies a sum above it (all P >= 0); a false alarm only
-      // costs the exact path.  Decided for the warp's 32 rows as a whole.
-      bool exact = (sb == 0);
-      if (!exact && !redo) exact = __any_sync(0xffffffffu, !(bsum <= kLazyLimit));
-      if (!exact && redo) {
-        bsum = softmax_pass<false>(t_sb, lim, c, -m * c, pk);
-        exact = __any_sync(0xffffffffu, !(bsum <= kLazyLimit));
-      }
-      if (exact) {
-        // Exact path (first sub-block, or the maximum is too low for some row of this
-        // warp): true row maximum, rescale l and O, publish, redo the exponentials.
-        const float m_new = fmaxf(m, row_max(t_sb, lim));
-        if (sb > 0) {
-          // O_i must be quiescent: PV_i(sb-1) complete; PV_i(sb) waits for this warp.
-          ok = wait_bounded(wctx, bar_o_done(i), static_cast<uint32_t>(sb - 1) & 1u, 0x700 + i);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          float alpha = ex2_approx((m - m_new) * c);
-          if (m == -INFINITY) alpha = 1.f;
-          l *= alpha;
-          rescale_o_columns(t_o, D / 32, alpha);
-        }
-        m = m_new;
-        grp.m[lane] = m_new;
-        __threadfence_block();
-        __syncwarp();
-        ++version;
-        if (lane == 0) grp.version = version;
-        bsum = softmax_pass<false>(t_sb, lim, c, (m == -INFINITY) ? 0.f : -m * c, pk);
-      }
-      l += bsum;
-      if (sb + 2 >= tile_nsb) {                        // my last sub-block: leave my share for the epilogue
-        grp.l_part[h][lane] = l;
-        grp.m_part[h][lane] = m;
-        __threadfence_block();
-      }
-      tmem_st_32x32b_x16(t_sb, pk);
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full(i, h));
-    }
-
-    if (ok && tile_nsb > 0) {
-      ok = wait_bounded(wctx, bar_o_final(i), 0, 0x600 + i);
-      ok = __all_sync(0xffffffffu, ok);
-      if (ok) {
         tc_fence_after();
         __threadfence_block();
         // Row sum = both warps' shares, each brought to the final maximum.
         float l_tot = 0.f, m_fin = -INFINITY;
 #pragma unroll
         for (int w2 = 0; w2 < 2; ++w2)
-          if (w2 < tile_nsb) m_fin = fmaxf(m_fin, grp.m_part[w2][lane]);
+          if (w2 < tile_nsb) m_fin = fmaxf(m_fin, grp.m_part[ib][w2][lane]);
 #pragma unroll
         for (int w2 = 0; w2 < 2; ++w2) {
           if (w2 < tile_nsb) {
-            const float mp = grp.m_part[w2][lane], lp = grp.l_part[w2][lane];
+            const float mp = grp.m_part[ib][w2][lane], lp = grp.l_part[ib][w2][lane];
             l_tot += (mp == -INFINITY) ? 0.f : lp * ex2_approx((mp - m_fin) * c);
           }
         }
         const float inv = ((l_tot == 0.f || l_tot != l_tot) ? 1.f : 1.f / l_tot) * args.o_scale;
-        // Each warp of the pair writes half of the head dimension.
-        __half* o_row = args.o + (static_cast<size_t>(bh) * seqlen + q_row) * D + h * (D / 2);
+        __half* o_row = args.o + (static_cast<size_t>(w.bh) * seqlen + q_row) * D + h * (D / 2);
 #pragma unroll
         for (int q = 0; q < D / 64; ++q) {
           uint32_t orow[32];
           tmem_ld_32x32b_x32(t_o + h * (D / 2) + 32 * q, orow);
           tmem_wait_ld();
+          if (q == D / 64 - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_o_free(i));      // the next item's PV may overwrite O_i
+          }
           if (q_row < seqlen) {
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
@@ -642,6 +752,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
           }
         }
+        ++items;
       }
     }
   }
@@ -649,7 +760,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == kMmaWarp0) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -661,33 +772,50 @@ static constexpr int smem_bytes_for() { return Cfg<D>::kSmemBytes; }
 
 template <int D, bool kCausal>
 static cudaError_t launch_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                              const KernelArgs& args, int n_pairs, int bh, cudaStream_t stream) {
+                              const KernelArgs& args, cudaStream_t stream) {
   auto kernel = &fa8_fwd_kernel<D, kCausal>;
   constexpr int smem = Cfg<D>::kSmemBytes;
   static bool attr_set[64] = {};
+  static int sm_count[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+  const bool cached = dev >= 0 && dev < 64;
+  if (!cached || !attr_set[dev]) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    int n = 0;
+    e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    if (cached) {
+      sm_count[dev] = n;
+      attr_set[dev] = true;
+    } else {
+      sm_count[0] = n;
+    }
   }
-  dim3 grid(n_pairs, bh, 1);
+  // Persistent grid: one CTA per SM (shared and tensor memory allow no more), each walking
+  // its share of the work units.
+  const int sms = cached ? sm_count[dev] : sm_count[0];
+#ifdef FA8_ONE_UNIT_PER_CTA
+  dim3 grid(args.n_units, 1, 1);
+  (void)sms;
+#else
+  dim3 grid(args.n_units < sms ? args.n_units : sms, 1, 1);
+#endif
   kernel<<<grid, kThreads, smem, stream>>>(tq, tk, tv, args);
   return cudaGetLastError();
 }
 
 cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
-                       const CUtensorMap& tv, const KernelArgs& args, int n_pairs, int bh,
-                       cudaStream_t stream) {
+                       const CUtensorMap& tv, const KernelArgs& args, cudaStream_t stream) {
   if (head_dim == 128) {
-    return causal ? launch_one<128, true>(tq, tk, tv, args, n_pairs, bh, stream)
-                  : launch_one<128, false>(tq, tk, tv, args, n_pairs, bh, stream);
+    return causal ? launch_one<128, true>(tq, tk, tv, args, stream)
+                  : launch_one<128, false>(tq, tk, tv, args, stream);
   }
   if (head_dim == 64) {
-    return causal ? launch_one<64, true>(tq, tk, tv, args, n_pairs, bh, stream)
-                  : launch_one<64, false>(tq, tk, tv, args, n_pairs, bh, stream);
+    return causal ? launch_one<64, true>(tq, tk, tv, args, stream)
+                  : launch_one<64, false>(tq, tk, tv, args, stream);
   }
   return cudaErrorInvalidValue;
 }

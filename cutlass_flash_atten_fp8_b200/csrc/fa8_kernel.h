@@ -13,15 +13,16 @@ namespace fa8 {
 struct KernelArgs {
   __half* o;                      // [batch*heads, seqlen, head_dim] fp16
   int seqlen;                     // queries == keys
+  int n_pairs;                    // ceil(seqlen / 256): pairs of 128-row query tiles per slice
+  int n_units;                    // work units of the persistent grid (see get_item)
   float scale_log2;               // softmax_scale * log2(e)
   float o_scale;                  // multiplies O/l (1 = reference behaviour)
   int* status;                    // optional device word; non-zero after a bounded wait expired
   unsigned long long timeout_ns;  // bound of every mbarrier wait
 };
 
-// Launches the forward kernel for head_dim in {64,128}; grid = (n_pairs, bh).
+// Launches the persistent forward kernel for head_dim in {64,128}.
 cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
-                       const CUtensorMap& tv, const KernelArgs& args, int n_pairs, int bh,
-                       cudaStream_t stream);
+                       const CUtensorMap& tv, const KernelArgs& args, cudaStream_t stream);
 
 }  // namespace fa8
