@@ -177,10 +177,11 @@ def run_reference_arm(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    per_step_budget = 4.0
+    # each step times a sample of the workload's slices; the whole run stays within ~3 minutes
+    per_step_budget = max(0.5, min(5.0, 150.0 / max(1, args.warmup + args.steps)))
     vals = []
     for i in range(args.warmup + args.steps):
-        r = cpu_attention_tflops(w, per_step_budget, 8, w.name)
+        r = cpu_attention_tflops(w, per_step_budget, w.n_slices, w.name)
         if i >= args.warmup:
             vals.append(r)
     v = sum(x["value"] for x in vals) / len(vals)

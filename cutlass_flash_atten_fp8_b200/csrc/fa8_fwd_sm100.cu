@@ -499,22 +499,26 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       auto slot_of = [&](uint32_t load) { return load & kSlotMask; };
       auto parity_of = [&](uint32_t load) { return (load >> kSlotShift) & 1u; };
       // S_i[h] = Q_i K_sb^T for sub-block sb = 2j+h: rows 64h..64h+63 of tile K_j;
-      // D/32 steps of K=32 bytes along the swizzled rows.
-      auto issue_qk = [&](uint32_t st, int h, uint32_t load) {
-        const uint64_t dq = dq_base + st * (2 * C::kTileBytes / 16);
-        const uint64_t dk = dk_base + (slot_of(load) * C::kTileBytes + h * kSubN * D) / 16;
-#pragma unroll
-        for (int k = 0; k < D / 32; ++k)
-          mma_f8_ss(t_s + h * kSubN, dq + 2u * k, dk + 2u * k, kIdescQK, k > 0);
+      // D/32 steps of K=32 bytes along the swizzled rows.  Operands are worked out by the
+      // caller before it starts waiting, so that the MMAs go out right after the wait.
+      auto desc_q = [&](uint32_t st) { return dq_base + st * (2 * C::kTileBytes / 16); };
+      auto desc_k = [&](uint32_t load, int h) {
+        return dk_base + (slot_of(load) * C::kTileBytes + h * kSubN * D) / 16;
       };
-      // O_i (+)= P_i(sb) V_sb: P is 128 rows x 64 e4m3 = 16 TMEM columns over S_i[h];
-      // the V^T tile is D rows of 128 key positions (K-major, 128-byte swizzle), of which
+      // The V^T tile is D rows of 128 key positions (K-major, 128-byte swizzle), of which
       // sub-block h covers bytes 64h..64h+63 of every row = K-steps 2h and 2h+1.
-      auto issue_pv = [&](int h, uint32_t load, bool acc) {
-        const uint64_t dv = dv_base + (slot_of(load) * C::kTileBytes) / 16 + 4u * h;
+      auto desc_v = [&](uint32_t load, int h) {
+        return dv_base + (slot_of(load) * C::kTileBytes) / 16 + 4u * h;
+      };
+      auto issue_qk = [&](uint32_t ts, uint64_t dq, uint64_t dk) {
+#pragma unroll
+        for (int k = 0; k < D / 32; ++k) mma_f8_ss(ts, dq + 2u * k, dk + 2u * k, kIdescQK, k > 0);
+      };
+      // O_i (+)= P_i(sb) V_sb: P is 128 rows x 64 e4m3 = 16 TMEM columns over S_i[h].
+      auto issue_pv = [&](uint32_t ts, uint64_t dv, bool acc) {
 #pragma unroll
         for (int k = 0; k < kSubN / 32; ++k)
-          mma_f8_ts(t_o, t_s + h * kSubN + 8u * k, dv + 2u * k, kIdescPV, (acc || k > 0) ? 1u : 0u);
+          mma_f8_ts(t_o, ts + 8u * k, dv + 2u * k, kIdescPV, (acc || k > 0) ? 1u : 0u);
       };
 
       for (int unit = blockIdx.x; unit < args.n_units && ok; unit += gridDim.x) {
@@ -543,15 +547,16 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           };
           if (nsb > 0) {
             const uint32_t st = qn & 1u;
+            const uint64_t dq = desc_q(st);
             // Prologue: the first two S need no P.
             wait_upto(0);
             if (ok) ok = wait_bounded(wctx, bar_q_full(i, st), (qn >> 1) & 1u, 0x300 + i);
             if (ok) {
               tc_fence_after();
-              issue_qk(st, 0, kv_base);
+              issue_qk(t_s, dq, desc_k(kv_base, 0));
               tc_commit(bar_s_full(i, 0));
               if (nsb > 1) {
-                issue_qk(st, 1, kv_base);
+                issue_qk(t_s + kSubN, dq, desc_k(kv_base, 1));
                 tc_commit(bar_s_full(i, 1));
               }
               if (nsb <= 2) tc_commit(bar_q_empty(i, st));
@@ -561,17 +566,21 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             for (int sb = 0; sb < nsb && ok; ++sb) {
               const int h = sb & 1;
               const uint32_t j2 = static_cast<uint32_t>(sb) & ~1u;          // 2j
-              wait_upto(sb + 2 < nsb ? j2 + 2 : j2 + 1);                     // V_j (and K_{j+1})
+              const bool has_qk = sb + 2 < nsb;
+              const uint32_t ts = t_s + h * kSubN;
+              const uint64_t dv = desc_v(kv_base + j2 + 1, h);
+              const uint64_t dk = desc_k(kv_base + j2 + 2, h);
+              wait_upto(has_qk ? j2 + 2 : j2 + 1);                           // V_j (and K_{j+1})
               if (ok) ok = wait_bounded(wctx, bar_p_full(i, h), (h ? p_cnt1 : p_cnt0) & 1u, 0x400 + i);
               if (sb == 0 && qn > 0 && ok)                                 // O_i of the previous item read out?
                 ok = wait_bounded(wctx, bar_o_free(i), (qn - 1) & 1u, 0x480 + i);
               if (!ok) break;
               tc_fence_after();
-              issue_pv(h, kv_base + j2 + 1, sb > 0);
+              issue_pv(ts, dv, sb > 0);
               tc_commit(bar_o_done(i));
               if (sb == nsb - 1) tc_commit(bar_o_final(i));
-              if (sb + 2 < nsb) {
-                issue_qk(st, h, kv_base + j2 + 2);
+              if (has_qk) {
+                issue_qk(ts, dq, dk);
                 tc_commit(bar_s_full(i, h));                                 // S_i[h] now holds sub-block sb+2
                 if (sb + 2 == nsb - 1) tc_commit(bar_q_empty(i, st));
               }
