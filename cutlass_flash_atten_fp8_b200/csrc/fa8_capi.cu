@@ -92,7 +92,7 @@ const char* fa8_last_error_detail(void) { return g_detail; }
 int fa8_supported(int32_t seqlen, int32_t head_dim, int32_t v_layout) {
   if (head_dim != 64 && head_dim != 128) return FA8_ERR_UNSUPPORTED;
   if (seqlen <= 0 || (seqlen % 16) != 0) return FA8_ERR_UNSUPPORTED;
-  if (v_layout != FA8_V_TRANSPOSED) return FA8_ERR_UNSUPPORTED;
+  if (v_layout != FA8_V_TRANSPOSED && v_layout != FA8_V_NATURAL) return FA8_ERR_UNSUPPORTED;
   return FA8_OK;
 }
 
@@ -114,8 +114,13 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   CUtensorMap tq, tk, tv;
   if (!make_map_3d(&tq, p->q, D, S, bh, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
   if (!make_map_3d(&tk, p->k, D, S, bh, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
-  // V^T: [bh, D, S]; a tile is D rows of 128 consecutive key positions.
-  if (!make_map_3d(&tv, p->v, S, D, bh, 128, static_cast<uint32_t>(D), CU_TENSOR_MAP_SWIZZLE_128B)) return FA8_ERR_CUDA;
+  if (p->v_layout == FA8_V_NATURAL) {
+    // V: [bh, S, D] like K; a tile is 128 key rows of D bytes.
+    if (!make_map_3d(&tv, p->v, D, S, bh, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
+  } else {
+    // V^T: [bh, D, S]; a tile is D rows of 128 consecutive key positions.
+    if (!make_map_3d(&tv, p->v, S, D, bh, 128, static_cast<uint32_t>(D), CU_TENSOR_MAP_SWIZZLE_128B)) return FA8_ERR_CUDA;
+  }
 
   fa8::KernelArgs args;
   args.o = static_cast<__half*>(p->o);
@@ -128,7 +133,7 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   const int64_t per_slice = p->is_causal ? (args.n_pairs + 1) / 2 : args.n_pairs;
   if (bh * per_slice > 0x7fffffff) return FA8_ERR_UNSUPPORTED;
   args.n_units = static_cast<int>(bh * per_slice);
-  cudaError_t e = fa8::launch_fwd(p->head_dim, p->is_causal != 0, tq, tk, tv, args,
+  cudaError_t e = fa8::launch_fwd(p->head_dim, p->is_causal != 0, p->v_layout == FA8_V_NATURAL, tq, tk, tv, args,
                                   static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess) {
     set_detail("kernel launch", cudaGetErrorString(e));

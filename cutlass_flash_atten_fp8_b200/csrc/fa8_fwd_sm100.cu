@@ -162,11 +162,24 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
 //                                              exponent is added in the integer domain
 // A value clamped from above reads 2^8 > kLazyLimit, so the caller's overflow test
 // still fires.
+// Constants of the exponential.  The part that depends on the row maximum is refreshed
+// only when the maximum changes; everything stays in registers across sub-blocks.
+struct ExpConsts {
+  f32x2_t c2, nm2;          // x = c*s + neg_mc, two lanes
+  float c128, nm128;        // the same map scaled into [0,1] for the saturating FMA
+  __device__ __forceinline__ void set_scale(float c) {
+    c2 = pack2(c, c);
+    c128 = c * (1.f / 128.f);
+  }
+  __device__ __forceinline__ void set_max(float neg_mc) {
+    nm2 = pack2(neg_mc, neg_mc);
+    nm128 = (neg_mc + 120.f) * (1.f / 128.f);
+  }
+};
+
 template <bool kAllowFma>
-__device__ __forceinline__ void softmax_chunk(uint32_t t_cols, int lim, float c, float neg_mc,
+__device__ __forceinline__ void softmax_chunk(uint32_t t_cols, int lim, const ExpConsts& k,
                                               uint32_t* pk, f32x2_t (&ls)[2]) {
-  const f32x2_t c2 = pack2(c, c), nm2 = pack2(neg_mc, neg_mc);
-  const float c128 = c * (1.f / 128.f), nm128 = (neg_mc + 120.f) * (1.f / 128.f);
   const f32x2_t k128 = pack2(128.f, 128.f);
   const f32x2_t magicp2 = pack2(12582912.f - 120.f, 12582912.f - 120.f);
   const f32x2_t neg1 = pack2(-1.f, -1.f);
@@ -188,7 +201,7 @@ __device__ __forceinline__ void softmax_chunk(uint32_t t_cols, int lim, float c,
       const float s0 = __uint_as_float(s[e + u]), s1 = __uint_as_float(s[e + u + 1]);
       const bool on_fma = kAllowFma && (((FA8_POLY_PAIR_MASK) >> ((e + u) / 2)) & 1);
       if (on_fma) {
-        const f32x2_t y2 = pack2(fma_sat(s0, c128, nm128), fma_sat(s1, c128, nm128));
+        const f32x2_t y2 = pack2(fma_sat(s0, k.c128, k.nm128), fma_sat(s1, k.c128, k.nm128));
         const f32x2_t t2 = fma2(y2, k128, magicp2);
         const f32x2_t nneg2 = fma2(t2, neg1, magicp2);          // -(n + 120)
         const f32x2_t f2 = fma2(y2, k128, nneg2);
@@ -202,7 +215,7 @@ __device__ __forceinline__ void softmax_chunk(uint32_t t_cols, int lim, float c,
         p[u + 1] = __int_as_float(__float_as_int(r1) + (__float_as_int(t1) << 23));
       } else {
         float x0, x1;
-        unpack2(fma2(pack2(s0, s1), c2, nm2), x0, x1);
+        unpack2(fma2(pack2(s0, s1), k.c2, k.nm2), x0, x1);
         p[u] = ex2_approx(x0);
         p[u + 1] = ex2_approx(x1);
       }
@@ -214,11 +227,11 @@ __device__ __forceinline__ void softmax_chunk(uint32_t t_cols, int lim, float c,
 
 // P of one 64-key sub-block of this thread's row -> pk[16]; returns the fp32 row sum.
 template <bool kAllowFma>
-__device__ __forceinline__ float softmax_pass(uint32_t t_sb, int lim, float c, float neg_mc,
+__device__ __forceinline__ float softmax_pass(uint32_t t_sb, int lim, const ExpConsts& k,
                                               uint32_t (&pk)[16]) {
   f32x2_t ls[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
-  softmax_chunk<kAllowFma>(t_sb, lim, c, neg_mc, pk, ls);
-  softmax_chunk<kAllowFma>(t_sb + 32, lim - 32, c, neg_mc, pk + 8, ls);
+  softmax_chunk<kAllowFma>(t_sb, lim, k, pk, ls);
+  softmax_chunk<kAllowFma>(t_sb + 32, lim - 32, k, pk + 8, ls);
   float a0, a1, a2, a3;
   unpack2(ls[0], a0, a1);
   unpack2(ls[1], a2, a3);
@@ -321,7 +334,7 @@ __device__ __forceinline__ bool get_item(const KernelArgs& a, int unit, int k, I
 
 }  // namespace
 
-template <int D, bool kCausal>
+template <int D, bool kCausal, bool kVNatural>
 __global__ void __launch_bounds__(kThreads, 1)
 fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const KernelArgs args) {
@@ -446,7 +459,8 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
           for (int j = 0; j < w.nb && ok; ++j) {
             load_kv(&tm_k, 0, j * kBlockN, w.bh);
-            load_kv(&tm_v, j * kBlockN, 0, w.bh);
+            if (kVNatural) load_kv(&tm_v, 0, j * kBlockN, w.bh);     // [keys, head_dim] rows
+            else load_kv(&tm_v, j * kBlockN, 0, w.bh);               // [head_dim, keys] rows
           }
         }
       }
@@ -482,7 +496,8 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (elect_one()) {
       const int i = warp - kMmaWarp0;
       constexpr uint32_t kIdescQK = umma_idesc(kTileM, kSubN);
-      constexpr uint32_t kIdescPV = umma_idesc(kTileM, D);
+      // V in its natural [keys, head_dim] layout is an MN-major B operand (bit 16).
+      constexpr uint32_t kIdescPV = umma_idesc(kTileM, D) | (kVNatural ? (1u << 16) : 0u);
       constexpr uint32_t kSlotMask = C::kSlots - 1;
       static_assert((C::kSlots & (C::kSlots - 1)) == 0, "ring size must be a power of two");
       constexpr int kSlotShift = (C::kSlots == 8) ? 3 : 4;
@@ -495,7 +510,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // Descriptors differ only in the 14-bit start-address field (units of 16 bytes).
       const uint64_t dq_base = umma_desc(s_q + i * C::kTileBytes, C::kQKSbo, C::kQKLayout);
       const uint64_t dk_base = umma_desc(s_ring, C::kQKSbo, C::kQKLayout);
-      const uint64_t dv_base = umma_desc(s_ring, 1024u, 2u);
+      const uint64_t dv_base = kVNatural ? umma_desc(s_ring, C::kQKSbo, C::kQKLayout) : umma_desc(s_ring, 1024u, 2u);
       auto slot_of = [&](uint32_t load) { return load & kSlotMask; };
       auto parity_of = [&](uint32_t load) { return (load >> kSlotShift) & 1u; };
       // S_i[h] = Q_i K_sb^T for sub-block sb = 2j+h: rows 64h..64h+63 of tile K_j;
@@ -507,8 +522,11 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       };
       // The V^T tile is D rows of 128 key positions (K-major, 128-byte swizzle), of which
       // sub-block h covers bytes 64h..64h+63 of every row = K-steps 2h and 2h+1.
+      // In the natural layout the tile is 128 key rows of D bytes (swizzled like K): a K-step
+      // of 32 keys is 32 rows further down.
+      constexpr uint32_t kVStep = kVNatural ? (32u * D / 16u) : 2u;   // descriptor units per 32 keys
       auto desc_v = [&](uint32_t load, int h) {
-        return dv_base + (slot_of(load) * C::kTileBytes) / 16 + 4u * h;
+        return dv_base + (slot_of(load) * C::kTileBytes) / 16 + 2u * kVStep * h;
       };
       auto issue_qk = [&](uint32_t ts, uint64_t dq, uint64_t dk) {
 #pragma unroll
@@ -518,7 +536,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       auto issue_pv = [&](uint32_t ts, uint64_t dv, bool acc) {
 #pragma unroll
         for (int k = 0; k < kSubN / 32; ++k)
-          mma_f8_ts(t_o, ts + 8u * k, dv + 2u * k, kIdescPV, (acc || k > 0) ? 1u : 0u);
+          mma_f8_ts(t_o, ts + 8u * k, dv + kVStep * k, kIdescPV, (acc || k > 0) ? 1u : 0u);
       };
 
       for (int unit = blockIdx.x; unit < args.n_units && ok; unit += gridDim.x) {
@@ -623,6 +641,9 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint32_t items = 0;          // work items of this tile so far: o_final[i] phase, l_part buffer
     uint32_t version = 0;        // last value of grp.version this warp has seen
     bool ok = true;
+    ExpConsts ek;
+    ek.set_scale(c);
+    ek.set_max(0.f);
 
     for (int unit = blockIdx.x; unit < args.n_units && ok; unit += gridDim.x) {
       for (int kk = 0; kk < kItemsPerUnit && ok; ++kk) {
@@ -649,7 +670,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           uint32_t pk[16];
           float bsum = 0.f;
           // Fast path: one pass, exponentials against the maximum known so far.
-          if (have_m) bsum = softmax_pass<true>(t_sb, lim, c, -m * c, pk);
+          if (have_m) bsum = softmax_pass<true>(t_sb, lim, ek, pk);
           // P(sb) may be handed over only after the partner has handed over P(sb-1): from
           // then on nobody else can raise the maximum before PV(sb) is issued.
           if (sb > 0)
@@ -673,7 +694,8 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 m = m_new;
                 version = v;
                 have_m = true;
-                bsum = softmax_pass<false>(t_sb, lim, c, -m * c, pk);
+                ek.set_max(-m * c);
+                bsum = softmax_pass<false>(t_sb, lim, ek, pk);
               }
               exact = __any_sync(0xffffffffu, !(bsum <= kLazyLimit));
             }
@@ -700,7 +722,8 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               version = grp.version + 1;
               __syncwarp();
               if (lane == 0) grp.version = version;
-              bsum = softmax_pass<false>(t_sb, lim, c, (m == -INFINITY) ? 0.f : -m * c, pk);
+              ek.set_max((m == -INFINITY) ? 0.f : -m * c);
+              bsum = softmax_pass<false>(t_sb, lim, ek, pk);
             }
           }
           l += bsum;
@@ -779,10 +802,10 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 template <int D>
 static constexpr int smem_bytes_for() { return Cfg<D>::kSmemBytes; }
 
-template <int D, bool kCausal>
+template <int D, bool kCausal, bool kVNatural>
 static cudaError_t launch_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                               const KernelArgs& args, cudaStream_t stream) {
-  auto kernel = &fa8_fwd_kernel<D, kCausal>;
+  auto kernel = &fa8_fwd_kernel<D, kCausal, kVNatural>;
   constexpr int smem = Cfg<D>::kSmemBytes;
   static bool attr_set[64] = {};
   static int sm_count[64] = {};
@@ -816,16 +839,19 @@ static cudaError_t launch_one(const CUtensorMap& tq, const CUtensorMap& tk, cons
   return cudaGetLastError();
 }
 
-cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
-                       const CUtensorMap& tv, const KernelArgs& args, cudaStream_t stream) {
+cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, const CUtensorMap& tq,
+                       const CUtensorMap& tk, const CUtensorMap& tv, const KernelArgs& args,
+                       cudaStream_t stream) {
+#define FA8_LAUNCH(DD, CC, VV) return launch_one<DD, CC, VV>(tq, tk, tv, args, stream)
   if (head_dim == 128) {
-    return causal ? launch_one<128, true>(tq, tk, tv, args, stream)
-                  : launch_one<128, false>(tq, tk, tv, args, stream);
+    if (causal) { if (v_natural) FA8_LAUNCH(128, true, true); else FA8_LAUNCH(128, true, false); }
+    else { if (v_natural) FA8_LAUNCH(128, false, true); else FA8_LAUNCH(128, false, false); }
   }
   if (head_dim == 64) {
-    return causal ? launch_one<64, true>(tq, tk, tv, args, stream)
-                  : launch_one<64, false>(tq, tk, tv, args, stream);
+    if (causal) { if (v_natural) FA8_LAUNCH(64, true, true); else FA8_LAUNCH(64, true, false); }
+    else { if (v_natural) FA8_LAUNCH(64, false, true); else FA8_LAUNCH(64, false, false); }
   }
+#undef FA8_LAUNCH
   return cudaErrorInvalidValue;
 }
 

@@ -22,7 +22,10 @@ struct KernelArgs {
 };
 
 // Launches the persistent forward kernel for head_dim in {64,128}.
-cudaError_t launch_fwd(int head_dim, bool causal, const CUtensorMap& tq, const CUtensorMap& tk,
-                       const CUtensorMap& tv, const KernelArgs& args, cudaStream_t stream);
+// v_natural: V is [slices, seqlen, head_dim] (tv describes it like K) instead of the
+// reference's transposed [slices, head_dim, seqlen].
+cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, const CUtensorMap& tq,
+                       const CUtensorMap& tk, const CUtensorMap& tv, const KernelArgs& args,
+                       cudaStream_t stream);
 
 }  // namespace fa8

@@ -77,6 +77,22 @@ def test_random_inputs_against_oracles(D, causal, S):
     assert_close_to_oracles(out, q8, k8, v8, causal, 1 / math.sqrt(D))
 
 
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("S", [64, 192, 256, 1024, 1360])
+def test_natural_v_layout(D, causal, S):
+    """V passed as [B,H,S,D] (no transpose by the caller): bitwise the same O as with the
+    reference's transposed V, and close to the oracles."""
+    d = dev()
+    q8, k8, v8 = (rand8(2, 3, S, D, seed=31 * S + D + i).to(d) for i in range(3))
+    scale = 1 / math.sqrt(D)
+    nat = flash_attention_v2_cutlass(q8, k8, v8.contiguous(), causal, scale, v_layout="natural")[0]
+    check_status(d)
+    tr = run_kernel(q8, k8, v8, causal, scale)
+    assert torch.equal(nat, tr)
+    assert_close_to_oracles(nat, q8, k8, v8, causal, scale)
+
+
 @pytest.mark.parametrize("S", [16, 48, 144, 272])
 def test_ragged_sequence_lengths(S):
     # not multiples of the 128-row tile (the reference needs multiples of 64, csrc/flash_attention.cu:594-597)
