@@ -343,7 +343,7 @@ def main():
             "algorithmic_hbm_gbs": w.hbm_bytes(n_local) / ms_step / 1e6,
             "clocks": clocks,
             "e2e": e2e,
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * world,
             "roofline": {"bound": "tensor", "achieved": tflops_gpu, "peak": fp8_peak, "unit": "TFLOP/s",
                          "frac": tflops_gpu / fp8_peak,
                          "traffic": NCU_TRAFFIC_BYTES.get(w.name),

@@ -55,7 +55,8 @@ def check_status(device: Optional[torch.device] = None) -> None:
 def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                                is_causal: bool = False, softmax_scale: float = 1.0, *,
                                v_layout: str = "transposed", o_scale: float = 1.0,
-                               out: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
+                               out: Optional[torch.Tensor] = None,
+                               return_lse: bool = False) -> List[torch.Tensor]:
     """FP8 attention forward.
 
     q, k: float8_e4m3fn [batch, heads, seqlen, head_dim], CUDA, contiguous.
@@ -66,6 +67,8 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     e4m3, csrc/flash_attention.cu:656).  The kernel is enqueued on the current
     stream; nothing synchronises (the reference blocks, :663-665) - call
     check_status() to synchronise and surface device-side errors.
+    return_lse=True appends the fp32 [batch, heads, seqlen] log-sum-exp of the scaled
+    scores (the reference reserves softmax_lse_ptr for it, csrc/flash.h:56, unused).
     """
     lib = _lib.load()
     _check_input(q, "q")
@@ -95,16 +98,18 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         _check_input(out, "out")
         if out.dtype != torch.float16 or tuple(out.shape) != (B, H, S, D) or out.device != q.device:
             raise RuntimeError("out must be a float16 CUDA tensor shaped like q")
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if return_lse else None
     p = _lib.Fa8FwdParams(
         q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=out.data_ptr(),
         batch=B, heads=H, seqlen=S, head_dim=D, softmax_scale=float(softmax_scale),
         is_causal=int(bool(is_causal)), v_layout=layout, o_scale=float(o_scale),
-        status_word=status_word(q.device).data_ptr())
+        status_word=status_word(q.device).data_ptr(),
+        softmax_lse=(lse.data_ptr() if lse is not None else None))
     with torch.cuda.device(q.device):
         rc = lib.fa8_fwd(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
     if rc != _lib.FA8_OK:
         raise RuntimeError(_lib.error_message(rc))
-    return [out]
+    return [out, lse] if return_lse else [out]
 
 
 class HostRunner:

@@ -74,7 +74,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 extern "C" {
 
-int fa8_version(void) { return 100; }
+int fa8_version(void) { return 101; }
 
 const char* fa8_error_string(int code) {
   switch (code) {
@@ -104,6 +104,7 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   if (!std::isfinite(p->o_scale)) return FA8_ERR_BAD_ARG;
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->o)) return FA8_ERR_BAD_ARG;
   if (p->status_word && (reinterpret_cast<uintptr_t>(p->status_word) & 3u)) return FA8_ERR_BAD_ARG;
+  if (p->softmax_lse && (reinterpret_cast<uintptr_t>(p->softmax_lse) & 3u)) return FA8_ERR_BAD_ARG;
   if (p->v_layout != FA8_V_TRANSPOSED && p->v_layout != FA8_V_NATURAL) return FA8_ERR_BAD_ARG;
   int sup = fa8_supported(p->seqlen, p->head_dim, p->v_layout);
   if (sup != FA8_OK) return sup;
@@ -128,6 +129,8 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   args.scale_log2 = p->softmax_scale * 1.4426950408889634f;
   args.o_scale = p->o_scale;
   args.status = p->status_word;
+  args.lse = p->softmax_lse;
+  args.softmax_scale = p->softmax_scale;
   args.timeout_ns = 2000000000ull;
   args.n_pairs = (p->seqlen + 255) / 256;
   const int64_t per_slice = p->is_causal ? (args.n_pairs + 1) / 2 : args.n_pairs;

@@ -762,6 +762,8 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
         const float inv = ((l_tot == 0.f || l_tot != l_tot) ? 1.f : 1.f / l_tot) * args.o_scale;
+        if (args.lse != nullptr && h == 0 && q_row < seqlen)    // log(sum exp(scale*s)) = scale*m + log(l)
+          args.lse[static_cast<size_t>(w.bh) * seqlen + q_row] = m_fin * args.softmax_scale + __logf(l_tot);
         __half* o_row = args.o + (static_cast<size_t>(w.bh) * seqlen + q_row) * D + h * (D / 2);
 #pragma unroll
         for (int q = 0; q < D / 64; ++q) {

@@ -17,6 +17,8 @@ struct KernelArgs {
   int n_units;                    // work units of the persistent grid (see get_item)
   float scale_log2;               // softmax_scale * log2(e)
   float o_scale;                  // multiplies O/l (1 = reference behaviour)
+  float* lse;                     // optional [batch*heads, seqlen] fp32: log-sum-exp of the scaled scores
+  float softmax_scale;            // as given by the caller (natural-log units, for lse)
   int* status;                    // optional device word; non-zero after a bounded wait expired
   unsigned long long timeout_ns;  // bound of every mbarrier wait
 };

@@ -1,5 +1,5 @@
 // Inline-PTX wrappers for the sm_100a features the FP8 attention kernel uses:
-// mbarrier, TMA tiled loads (no multicast anywhere), tcgen05 MMA / TMEM
+// mbarrier, TMA tiled loads (every CTA fetches its own tiles), tcgen05 MMA / TMEM
 // alloc / ld / st / commit, and a few scalar helpers.  Every wrapper is a thin
 // spelling of one PTX instruction; policy (who waits on what) lives in the
 // kernel file.

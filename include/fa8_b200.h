@@ -61,6 +61,10 @@ typedef struct fa8_fwd_params {
                           softmax_scale */
   int32_t* status_word; /* optional device int32, zero before the call; the kernel stores a
                            non-zero code there if one of its bounded waits runs out */
+  float* softmax_lse;   /* optional device fp32 [batch, heads, seqlen]: log(sum_j exp(softmax_scale *
+                           s_ij)) per query row, written when not NULL.  The reference carries the
+                           pointer (softmax_lse_ptr, csrc/flash.h:56) but never fills it
+                           (csrc/flash_attention.cu:310-311 passes nullptr). */
 } fa8_fwd_params;
 
 /* Enqueues the forward on `cuda_stream` (a cudaStream_t; NULL = default stream)
@@ -85,7 +89,8 @@ const char* fa8_error_string(int code);
 /* Text of the last CUDA failure seen by the calling thread (empty string if none). */
 const char* fa8_last_error_detail(void);
 
-/* ABI version of this header: major*100 + minor. */
+/* ABI version of this header: major*100 + minor (101 added softmax_lse at the end of
+ * fa8_fwd_params). */
 int fa8_version(void);
 
 #ifdef __cplusplus

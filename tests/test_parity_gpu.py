@@ -113,6 +113,25 @@ def test_tiny_config_with_per_tensor_scales():
     assert m["rel_l2"] <= REL_L2_FP32 and m["max_abs"] <= MAX_ABS_FRAC_FP32 * m["max_ref"], m
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_log_sum_exp_output(causal):
+    # lse_i = log(sum_j exp(scale * s_ij)); the scores are exact fp32 sums of e4m3 products
+    d = dev()
+    B, H, S, D = 2, 2, 704, 128
+    q8, k8, v8 = (rand8(B, H, S, D, seed=900 + i) for i in range(3))
+    scale = 1 / math.sqrt(D)
+    out, lse = flash_attention_v2_cutlass(q8.to(d), k8.to(d), v8.to(d), causal, scale, v_layout="natural",
+                                          return_lse=True)
+    check_status(d)
+    s = torch.matmul(q8.float(), k8.float().transpose(2, 3)) * scale
+    if causal:
+        s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool).tril(), float("-inf"))
+    want = torch.logsumexp(s, dim=-1)
+    assert tuple(lse.shape) == (B, H, S) and lse.dtype == torch.float32
+    assert float((lse.cpu() - want).abs().max()) <= 2e-3
+    assert torch.equal(out, run_kernel(q8, k8, v8, causal, scale))
+
+
 def test_known_answers():
     S, D = 512, 128
     q8, k8 = rand8(1, 2, S, D, seed=1), rand8(1, 2, S, D, seed=2)
