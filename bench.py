@@ -210,6 +210,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", action="store_true", help="also time the optional NCCL gather of O on rank 0")
+    ap.add_argument("--v-layout", default="transposed", choices=["transposed", "natural"],
+                    help="V as the reference passes it ([.., head_dim, seqlen]) or untransposed")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end, CPU-baseline, FP8-GEMM and reference-kernel legs (profiling runs)")
     args = ap.parse_args()
@@ -247,14 +249,16 @@ def main():
         wl = w
         total_slices = w.n_slices
     n_local = hi - lo
-    q8, k8, vt8, (dq, dk, dv) = synth.make_qkv(wl, device, lo, hi)
+    natural = args.v_layout == "natural"
+    q8, k8, vt8, (dq, dk, dv) = synth.make_qkv(wl, device, lo, hi, transpose_v=not natural)
     S, D = w.seqlen, w.head_dim
-    q4, k4, v4 = q8.view(1, n_local, S, D), k8.view(1, n_local, S, D), vt8.view(1, n_local, D, S)
+    q4, k4 = q8.view(1, n_local, S, D), k8.view(1, n_local, S, D)
+    v4 = vt8.view(1, n_local, S, D) if natural else vt8.view(1, n_local, D, S)
     out = torch.empty((1, n_local, S, D), dtype=torch.float16, device=device)
     scale = w.softmax_scale * dq * dk
 
     def step():
-        flash_attention_v2_cutlass(q4, k4, v4, w.causal, scale, o_scale=dv, out=out)
+        flash_attention_v2_cutlass(q4, k4, v4, w.causal, scale, o_scale=dv, out=out, v_layout=args.v_layout)
 
     def barrier():
         if world > 1:
@@ -298,11 +302,11 @@ def main():
     runner = HostRunner(device)
     hq, hk, hv = (torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in (q4, k4, v4))
     for _ in range(2):
-        runner(hq, hk, hv, w.causal, scale, o_scale=dv)
+        runner(hq, hk, hv, w.causal, scale, o_scale=dv, v_layout=args.v_layout)
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.e2e_steps):
-        runner(hq, hk, hv, w.causal, scale, o_scale=dv)
+        runner(hq, hk, hv, w.causal, scale, o_scale=dv, v_layout=args.v_layout)
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     if world > 1:
@@ -333,7 +337,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
             "config": {"workload": w.name, "batch": w.batch, "heads": w.heads, "seqlen": w.seqlen, "head_dim": w.head_dim,
-                       "causal": w.causal, "outliers": w.outliers, "slices_per_gpu": n_local, "v_layout": "transposed",
+                       "causal": w.causal, "outliers": w.outliers, "slices_per_gpu": n_local, "v_layout": args.v_layout,
                        "out_dtype": "fp16", "parallelism": f"(batch x head) shards x{world}, no collective",
                        "l2": f"inputs+output {w.hbm_bytes(n_local) / 1e6:.0f} MB per step exceed the 126 MB L2"},
             "tflops_per_gpu": tflops_gpu,
@@ -353,7 +357,8 @@ def main():
         if gather_ms is not None:
             line["gather_o_ms"] = gather_ms
         if world == 1:
-            line["reference_kernel"] = reference_kernel_tflops(w, q4, k4, v4, args.steps)
+            line["reference_kernel"] = (reference_kernel_tflops(w, q4, k4, v4, args.steps) if not natural
+                                        else {"unavailable": "the reference kernel needs V transposed"})
             if not args.no_cpu_baseline:
                 line["cpu_baseline"] = cpu_attention_tflops(w, 12.0, w.n_slices, w.name)
                 line["cpu_baseline"].pop("seconds_per_slice", None)

@@ -21,7 +21,7 @@ FA8_V_NATURAL = 1
 
 # Every symbol include/fa8_b200.h declares.
 EXPORTED_SYMBOLS = ("fa8_fwd", "fa8_check_status", "fa8_supported", "fa8_error_string",
-                    "fa8_last_error_detail", "fa8_version")
+                    "fa8_last_error_detail", "fa8_version", "fa8_selftest_expired_wait")
 
 
 class Fa8FwdParams(ctypes.Structure):
@@ -51,6 +51,8 @@ def load() -> ctypes.CDLL:
     lib.fa8_fwd.restype = ctypes.c_int
     lib.fa8_check_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
     lib.fa8_check_status.restype = ctypes.c_int
+    lib.fa8_selftest_expired_wait.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p]
+    lib.fa8_selftest_expired_wait.restype = ctypes.c_int
     lib.fa8_supported.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.fa8_supported.restype = ctypes.c_int
     lib.fa8_error_string.argtypes = [ctypes.c_int]

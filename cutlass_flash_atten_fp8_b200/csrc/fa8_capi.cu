@@ -145,6 +145,18 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   return FA8_OK;
 }
 
+int fa8_selftest_expired_wait(int32_t* status_word, uint32_t limit_us, void* cuda_stream) {
+  g_detail[0] = '\0';
+  if (!status_word || (reinterpret_cast<uintptr_t>(status_word) & 3u)) return FA8_ERR_BAD_ARG;
+  if (limit_us == 0 || limit_us > 1000000u) return FA8_ERR_BAD_ARG;     // at most one second
+  cudaError_t e = fa8::launch_expired_wait(status_word, 1000ull * limit_us, static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) {
+    set_detail("kernel launch", cudaGetErrorString(e));
+    return FA8_ERR_CUDA;
+  }
+  return FA8_OK;
+}
+
 int fa8_check_status(const int32_t* status_word, void* cuda_stream, int32_t* code_out) {
   g_detail[0] = '\0';
   if (!status_word) return FA8_ERR_BAD_ARG;

@@ -127,12 +127,12 @@ __device__ __forceinline__ bool wait_bounded(const WaitCtx& w, uint32_t bar, uin
 
 // ------------------------------------------------------------ softmax passes
 // Which of the 16 element pairs of a 32-column chunk take their exponential on the FMA
-// pipe instead of the special-function unit (bit p = pair p).
-#ifndef FA8_MMA_IDLE_SLEEP_NS
-#define FA8_MMA_IDLE_SLEEP_NS 0   // pause of the MMA lane between two fruitless polls of the P barriers
-#endif
+// pipe instead of the special-function unit (bit p = pair p).  Measured on B200: moving a
+// quarter of the exponentials over (0x1111) costs as many issue slots as it frees
+// special-function cycles and is no faster at head_dim 128, slower at 64 and with a causal
+// mask, so the default keeps them all on ex2.
 #ifndef FA8_POLY_PAIR_MASK
-#define FA8_POLY_PAIR_MASK 0x1111
+#define FA8_POLY_PAIR_MASK 0x0000
 #endif
 // P may grow to kLazyLimit (<= 448, the e4m3 maximum, with room for the polynomial
 // path's clamp at 2^8) before the row maximum is raised.
@@ -798,6 +798,27 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+// Self-test of the bounded wait: one CTA waits on an mbarrier that nobody ever arrives on.
+// The wait gives up after `limit_ns`, records 0x7e57 in the status word and the kernel
+// returns normally, leaving the context usable.
+__global__ void fa8_expired_wait_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const WaitCtx w{&abort_flag, status, limit_ns};
+  wait_bounded(w, smem_u32(&bar), 0, 0x7e57);
+}
+
+cudaError_t launch_expired_wait(int* status, unsigned long long limit_ns, cudaStream_t stream) {
+  fa8_expired_wait_kernel<<<1, 32, 0, stream>>>(status, limit_ns);
+  return cudaGetLastError();
 }
 
 // ------------------------------------------------------------------- launcher

@@ -30,4 +30,7 @@ cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, const CUtensor
                        const CUtensorMap& tk, const CUtensorMap& tv, const KernelArgs& args,
                        cudaStream_t stream);
 
+// One warp waits (bounded by limit_ns) on a barrier that never completes; see fa8_selftest_expired_wait.
+cudaError_t launch_expired_wait(int* status, unsigned long long limit_ns, cudaStream_t stream);
+
 }  // namespace fa8

@@ -78,6 +78,14 @@ int fa8_fwd(const fa8_fwd_params* params, void* cuda_stream);
  * (csrc/flash_attention.cu:663-665). */
 int fa8_check_status(const int32_t* status_word, void* cuda_stream, int32_t* code_out);
 
+/* Failure-detection self-test (no counterpart in the reference, whose only error path is
+ * exit(), include/attention_api.cuh:20-29): enqueues a one-warp kernel that waits on a barrier
+ * nobody completes, using the same bounded wait as the attention kernel.  After `limit_us`
+ * microseconds (1..1000000) the wait gives up, the kernel stores 0x7e57 in *status_word and
+ * returns; fa8_check_status then reports FA8_ERR_DEVICE_TIMEOUT and the CUDA context stays
+ * usable.  Nothing faults, traps or hangs. */
+int fa8_selftest_expired_wait(int32_t* status_word, uint32_t limit_us, void* cuda_stream);
+
 /* Says whether fa8_fwd implements this shape: FA8_OK or FA8_ERR_UNSUPPORTED.  Replaces the
  * head_dim switch of the reference (csrc/static_switch.h:50-77). */
 int fa8_supported(int32_t seqlen, int32_t head_dim, int32_t v_layout);
