@@ -31,7 +31,7 @@ class Fa8FwdParams(ctypes.Structure):
         ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seqlen", ctypes.c_int32),
         ("head_dim", ctypes.c_int32), ("softmax_scale", ctypes.c_float), ("is_causal", ctypes.c_int32),
         ("v_layout", ctypes.c_int32), ("o_scale", ctypes.c_float), ("status_word", ctypes.c_void_p),
-        ("softmax_lse", ctypes.c_void_p),
+        ("softmax_lse", ctypes.c_void_p), ("heads_kv", ctypes.c_int32),
     ]
 
 

@@ -59,7 +59,9 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
                                return_lse: bool = False) -> List[torch.Tensor]:
     """FP8 attention forward.
 
-    q, k: float8_e4m3fn [batch, heads, seqlen, head_dim], CUDA, contiguous.
+    q, k: float8_e4m3fn [batch, heads, seqlen, head_dim], CUDA, contiguous.  k and v may have
+          fewer heads (a divisor of q's): grouped-query attention, query head h reading K/V
+          head h // (heads // heads_kv).
     v:    float8_e4m3fn, transposed [batch, heads, head_dim, seqlen] as the reference
           requires (test.py:71), or [batch, heads, seqlen, head_dim] with
           v_layout="natural".
@@ -82,12 +84,14 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         if t.device != q.device:
             raise RuntimeError("q, k and v must be on the same device")
     B, H, S, D = q.shape
-    if tuple(k.shape) != (B, H, S, D):
-        raise RuntimeError(f"k must have the shape of q {tuple(q.shape)}, got {tuple(k.shape)}")
+    Hk = k.shape[1]
+    if tuple(k.shape) != (B, Hk, S, D) or Hk < 1 or H % Hk != 0:
+        raise RuntimeError(f"k must be [batch, heads_kv, seqlen, head_dim] with heads_kv dividing {H}; "
+                           f"q is {tuple(q.shape)}, k is {tuple(k.shape)}")
     if v_layout == "transposed":
-        want_v, layout = (B, H, D, S), _lib.FA8_V_TRANSPOSED
+        want_v, layout = (B, Hk, D, S), _lib.FA8_V_TRANSPOSED
     elif v_layout == "natural":
-        want_v, layout = (B, H, S, D), _lib.FA8_V_NATURAL
+        want_v, layout = (B, Hk, S, D), _lib.FA8_V_NATURAL
     else:
         raise RuntimeError("v_layout must be 'transposed' or 'natural'")
     if tuple(v.shape) != want_v:
@@ -104,7 +108,7 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         batch=B, heads=H, seqlen=S, head_dim=D, softmax_scale=float(softmax_scale),
         is_causal=int(bool(is_causal)), v_layout=layout, o_scale=float(o_scale),
         status_word=status_word(q.device).data_ptr(),
-        softmax_lse=(lse.data_ptr() if lse is not None else None))
+        softmax_lse=(lse.data_ptr() if lse is not None else None), heads_kv=Hk)
     with torch.cuda.device(q.device):
         rc = lib.fa8_fwd(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
     if rc != _lib.FA8_OK:

@@ -74,7 +74,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 extern "C" {
 
-int fa8_version(void) { return 101; }
+int fa8_version(void) { return 102; }
 
 const char* fa8_error_string(int code) {
   switch (code) {
@@ -109,18 +109,21 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   int sup = fa8_supported(p->seqlen, p->head_dim, p->v_layout);
   if (sup != FA8_OK) return sup;
   const int64_t bh = static_cast<int64_t>(p->batch) * p->heads;
+  const int32_t heads_kv = p->heads_kv > 0 ? p->heads_kv : p->heads;
+  if (heads_kv > p->heads || p->heads % heads_kv != 0) return FA8_ERR_BAD_ARG;
+  const int64_t bh_kv = static_cast<int64_t>(p->batch) * heads_kv;
 
   const uint64_t S = static_cast<uint64_t>(p->seqlen), D = static_cast<uint64_t>(p->head_dim);
   const CUtensorMapSwizzle sw_qk = (p->head_dim == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap tq, tk, tv;
   if (!make_map_3d(&tq, p->q, D, S, bh, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
-  if (!make_map_3d(&tk, p->k, D, S, bh, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
+  if (!make_map_3d(&tk, p->k, D, S, bh_kv, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
   if (p->v_layout == FA8_V_NATURAL) {
     // V: [bh, S, D] like K; a tile is 128 key rows of D bytes.
-    if (!make_map_3d(&tv, p->v, D, S, bh, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
+    if (!make_map_3d(&tv, p->v, D, S, bh_kv, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
   } else {
     // V^T: [bh, D, S]; a tile is D rows of 128 consecutive key positions.
-    if (!make_map_3d(&tv, p->v, S, D, bh, 128, static_cast<uint32_t>(D), CU_TENSOR_MAP_SWIZZLE_128B)) return FA8_ERR_CUDA;
+    if (!make_map_3d(&tv, p->v, S, D, bh_kv, 128, static_cast<uint32_t>(D), CU_TENSOR_MAP_SWIZZLE_128B)) return FA8_ERR_CUDA;
   }
 
   fa8::KernelArgs args;
@@ -130,6 +133,8 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   args.o_scale = p->o_scale;
   args.status = p->status_word;
   args.lse = p->softmax_lse;
+  args.heads = p->heads;
+  args.heads_kv = heads_kv;
   args.softmax_scale = p->softmax_scale;
   args.timeout_ns = 2000000000ull;
   args.n_pairs = (p->seqlen + 255) / 256;

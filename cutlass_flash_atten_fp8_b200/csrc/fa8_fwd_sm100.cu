@@ -457,10 +457,13 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               }
             }
           }
+          // Grouped-query attention: query head h of a batch entry reads K/V head h / group.
+          const int b_idx = w.bh / args.heads;
+          const int kv_bh = b_idx * args.heads_kv + (w.bh - b_idx * args.heads) / (args.heads / args.heads_kv);
           for (int j = 0; j < w.nb && ok; ++j) {
-            load_kv(&tm_k, 0, j * kBlockN, w.bh);
-            if (kVNatural) load_kv(&tm_v, 0, j * kBlockN, w.bh);     // [keys, head_dim] rows
-            else load_kv(&tm_v, j * kBlockN, 0, w.bh);               // [head_dim, keys] rows
+            load_kv(&tm_k, 0, j * kBlockN, kv_bh);
+            if (kVNatural) load_kv(&tm_v, 0, j * kBlockN, kv_bh);    // [keys, head_dim] rows
+            else load_kv(&tm_v, j * kBlockN, 0, kv_bh);              // [head_dim, keys] rows
           }
         }
       }

@@ -13,6 +13,8 @@ namespace fa8 {
 struct KernelArgs {
   __half* o;                      // [batch*heads, seqlen, head_dim] fp16
   int seqlen;                     // queries == keys
+  int heads;                      // query heads per batch entry
+  int heads_kv;                   // K/V heads per batch entry (divides heads)
   int n_pairs;                    // ceil(seqlen / 256): pairs of 128-row query tiles per slice
   int n_units;                    // work units of the persistent grid (see get_item)
   float scale_log2;               // softmax_scale * log2(e)

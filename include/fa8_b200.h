@@ -65,6 +65,11 @@ typedef struct fa8_fwd_params {
                            s_ij)) per query row, written when not NULL.  The reference carries the
                            pointer (softmax_lse_ptr, csrc/flash.h:56) but never fills it
                            (csrc/flash_attention.cu:310-311 passes nullptr). */
+  int32_t heads_kv;     /* heads of K and V (grouped-query attention): 0 or `heads` = one K/V head per
+                           query head, otherwise a divisor of `heads`; query head h reads K/V head
+                           h / (heads / heads_kv).  K and V are then [batch, heads_kv, ...].  The
+                           reference reserves k_head / h_h_k_ratio for this (csrc/flash.h:36-45) but
+                           its kernel ignores them (csrc/flash_attention.cu:364-379). */
 } fa8_fwd_params;
 
 /* Enqueues the forward on `cuda_stream` (a cudaStream_t; NULL = default stream)
@@ -97,8 +102,8 @@ const char* fa8_error_string(int code);
 /* Text of the last CUDA failure seen by the calling thread (empty string if none). */
 const char* fa8_last_error_detail(void);
 
-/* ABI version of this header: major*100 + minor (101 added softmax_lse at the end of
- * fa8_fwd_params). */
+/* ABI version of this header: major*100 + minor (101 added softmax_lse, 102 heads_kv, both at the
+ * end of fa8_fwd_params). */
 int fa8_version(void);
 
 #ifdef __cplusplus

@@ -132,6 +132,24 @@ def test_log_sum_exp_output(causal):
     assert torch.equal(out, run_kernel(q8, k8, v8, causal, scale))
 
 
+@pytest.mark.parametrize("Hk", [1, 2])
+@pytest.mark.parametrize("causal", [False, True])
+def test_grouped_query_attention(Hk, causal):
+    # 4 query heads share Hk key/value heads: same as expanding K and V
+    d = dev()
+    B, H, S, D = 2, 4, 640, 128
+    q8 = rand8(B, H, S, D, seed=70)
+    k8, v8 = rand8(B, Hk, S, D, seed=71), rand8(B, Hk, S, D, seed=72)
+    scale = 1 / math.sqrt(D)
+    got = flash_attention_v2_cutlass(q8.to(d), k8.to(d), v8.to(d).transpose(2, 3).contiguous(), causal, scale)[0]
+    check_status(d)
+    rep = H // Hk
+    want = run_kernel(q8, k8.repeat_interleave(rep, dim=1), v8.repeat_interleave(rep, dim=1), causal, scale)
+    assert torch.equal(got, want)
+    with pytest.raises(RuntimeError, match="heads_kv"):
+        flash_attention_v2_cutlass(q8.to(d), rand8(B, 3, S, D, seed=73).to(d), v8.to(d), causal, scale)
+
+
 def test_known_answers():
     S, D = 512, 128
     q8, k8 = rand8(1, 2, S, D, seed=1), rand8(1, 2, S, D, seed=2)
