@@ -147,6 +147,28 @@ def fp8_gemm_peak(device) -> float | None:
         return None
 
 
+def quantize_rate(device, peaks):
+    """HBM rate of the fp16 -> e4m3 per-tensor quantisation pre-pass (two kernels, 5 bytes of
+    algorithmic traffic per element) on a 1 GiB tensor; reported beside the attention result."""
+    try:
+        from cutlass_flash_atten_fp8_b200 import quantize_e4m3
+        n = 512 * 1024 * 1024
+        x = torch.randn(n // 4, device=device).half().repeat(4)
+        for _ in range(2):
+            quantize_e4m3(x)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            quantize_e4m3(x)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 5
+        gbs = 5.0 * n / ms / 1e6
+        return {"elements": n, "ms": ms, "algorithmic_gbs": gbs, "hbm_peak_gbs": peaks["hbm_gbs"], "frac": gbs / peaks["hbm_gbs"]}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:120]}"}
+
+
 def reference_kernel_tflops(w, q8, k8, vt8, steps: int):
     """Optional: the reference's own Ada kernel (built by oracle/build_ref.sh into oracle/_ref,
     sm_89 PTX assembled for sm_100) timed on this GPU on the same inputs.  Reported beside the
@@ -361,6 +383,7 @@ def main():
         if gather_ms is not None:
             line["gather_o_ms"] = gather_ms
         if world == 1:
+            line["quantize_prepass"] = quantize_rate(device, peaks)
             line["reference_kernel"] = (reference_kernel_tflops(w, q4, k4, v4, args.steps) if not natural
                                         else {"unavailable": "the reference kernel needs V transposed"})
             if not args.no_cpu_baseline:

@@ -18,10 +18,13 @@ FA8_ERR_DEVICE_TIMEOUT = -4
 
 FA8_V_TRANSPOSED = 0
 FA8_V_NATURAL = 1
+FA8_DTYPE_FP16 = 0
+FA8_DTYPE_BF16 = 1
 
 # Every symbol include/fa8_b200.h declares.
 EXPORTED_SYMBOLS = ("fa8_fwd", "fa8_check_status", "fa8_supported", "fa8_error_string",
-                    "fa8_last_error_detail", "fa8_version", "fa8_selftest_expired_wait")
+                    "fa8_last_error_detail", "fa8_version", "fa8_selftest_expired_wait",
+                    "fa8_quantize_e4m3")
 
 
 class Fa8FwdParams(ctypes.Structure):
@@ -32,6 +35,7 @@ class Fa8FwdParams(ctypes.Structure):
         ("head_dim", ctypes.c_int32), ("softmax_scale", ctypes.c_float), ("is_causal", ctypes.c_int32),
         ("v_layout", ctypes.c_int32), ("o_scale", ctypes.c_float), ("status_word", ctypes.c_void_p),
         ("softmax_lse", ctypes.c_void_p), ("heads_kv", ctypes.c_int32),
+        ("descale_q", ctypes.c_void_p), ("descale_k", ctypes.c_void_p), ("descale_v", ctypes.c_void_p),
     ]
 
 
@@ -53,6 +57,9 @@ def load() -> ctypes.CDLL:
     lib.fa8_check_status.restype = ctypes.c_int
     lib.fa8_selftest_expired_wait.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p]
     lib.fa8_selftest_expired_wait.restype = ctypes.c_int
+    lib.fa8_quantize_e4m3.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64,
+                                      ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    lib.fa8_quantize_e4m3.restype = ctypes.c_int
     lib.fa8_supported.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.fa8_supported.restype = ctypes.c_int
     lib.fa8_error_string.argtypes = [ctypes.c_int]

@@ -56,7 +56,10 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
                                is_causal: bool = False, softmax_scale: float = 1.0, *,
                                v_layout: str = "transposed", o_scale: float = 1.0,
                                out: Optional[torch.Tensor] = None,
-                               return_lse: bool = False) -> List[torch.Tensor]:
+                               return_lse: bool = False,
+                               descale_q: Optional[torch.Tensor] = None,
+                               descale_k: Optional[torch.Tensor] = None,
+                               descale_v: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
     """FP8 attention forward.
 
     q, k: float8_e4m3fn [batch, heads, seqlen, head_dim], CUDA, contiguous.  k and v may have
@@ -69,6 +72,8 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     e4m3, csrc/flash_attention.cu:656).  The kernel is enqueued on the current
     stream; nothing synchronises (the reference blocks, :663-665) - call
     check_status() to synchronise and surface device-side errors.
+    descale_q/k/v: optional one-element fp32 CUDA tensors (as returned by quantize_e4m3);
+    the kernel folds them into the softmax scale and into O without a host round trip.
     return_lse=True appends the fp32 [batch, heads, seqlen] log-sum-exp of the scaled
     scores (the reference reserves softmax_lse_ptr for it, csrc/flash.h:56, unused).
     """
@@ -102,18 +107,44 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         _check_input(out, "out")
         if out.dtype != torch.float16 or tuple(out.shape) != (B, H, S, D) or out.device != q.device:
             raise RuntimeError("out must be a float16 CUDA tensor shaped like q")
+    for name, t in (("descale_q", descale_q), ("descale_k", descale_k), ("descale_v", descale_v)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != 1 or t.device != q.device):
+            raise RuntimeError(f"{name} must be a one-element float32 tensor on q's device")
     lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if return_lse else None
     p = _lib.Fa8FwdParams(
         q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=out.data_ptr(),
         batch=B, heads=H, seqlen=S, head_dim=D, softmax_scale=float(softmax_scale),
         is_causal=int(bool(is_causal)), v_layout=layout, o_scale=float(o_scale),
         status_word=status_word(q.device).data_ptr(),
-        softmax_lse=(lse.data_ptr() if lse is not None else None), heads_kv=Hk)
+        softmax_lse=(lse.data_ptr() if lse is not None else None), heads_kv=Hk,
+        descale_q=(descale_q.data_ptr() if descale_q is not None else None),
+        descale_k=(descale_k.data_ptr() if descale_k is not None else None),
+        descale_v=(descale_v.data_ptr() if descale_v is not None else None))
     with torch.cuda.device(q.device):
         rc = lib.fa8_fwd(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
     if rc != _lib.FA8_OK:
         raise RuntimeError(_lib.error_message(rc))
     return [out, lse] if return_lse else [out]
+
+
+def quantize_e4m3(x: torch.Tensor):
+    """Per-tensor amax quantisation of a contiguous fp16 / bf16 CUDA tensor:
+    returns (x8, descale) with x8 = e4m3(x * 448 / max|x|) shaped like x and descale a
+    one-element fp32 tensor (x ~= descale * x8).  Stream-ordered, two HBM-bound kernels;
+    stands where the reference's callers cast with torch (test.py:20-22, 68-70)."""
+    lib = _lib.load()
+    _check_input(x, "x")
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError(f"x must be float16 or bfloat16, got {x.dtype}")
+    x8 = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    scal = torch.empty(2, dtype=torch.float32, device=x.device)       # [amax, descale]
+    with torch.cuda.device(x.device):
+        rc = lib.fa8_quantize_e4m3(x.data_ptr(), _lib.FA8_DTYPE_BF16 if x.dtype == torch.bfloat16 else _lib.FA8_DTYPE_FP16,
+                                   x8.data_ptr(), x.numel(), scal.data_ptr(), scal.data_ptr() + 4,
+                                   torch.cuda.current_stream(x.device).cuda_stream)
+    if rc != _lib.FA8_OK:
+        raise RuntimeError(_lib.error_message(rc))
+    return x8, scal[1:2]
 
 
 class HostRunner:

@@ -16,7 +16,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 REPO_DIR = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libfa8_b200.so")
-SOURCES = ["fa8_fwd_sm100.cu", "fa8_capi.cu"]
+SOURCES = ["fa8_fwd_sm100.cu", "fa8_quant.cu", "fa8_capi.cu"]
 HEADERS = ["fa8_kernel.h", "ptx_sm100.cuh", os.path.join(REPO_DIR, "include", "fa8_b200.h")]
 
 

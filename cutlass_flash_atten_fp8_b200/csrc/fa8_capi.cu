@@ -74,7 +74,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 extern "C" {
 
-int fa8_version(void) { return 102; }
+int fa8_version(void) { return 103; }
 
 const char* fa8_error_string(int code) {
   switch (code) {
@@ -105,6 +105,8 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->o)) return FA8_ERR_BAD_ARG;
   if (p->status_word && (reinterpret_cast<uintptr_t>(p->status_word) & 3u)) return FA8_ERR_BAD_ARG;
   if (p->softmax_lse && (reinterpret_cast<uintptr_t>(p->softmax_lse) & 3u)) return FA8_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(p->descale_q) | reinterpret_cast<uintptr_t>(p->descale_k) |
+       reinterpret_cast<uintptr_t>(p->descale_v)) & 3u) return FA8_ERR_BAD_ARG;
   if (p->v_layout != FA8_V_TRANSPOSED && p->v_layout != FA8_V_NATURAL) return FA8_ERR_BAD_ARG;
   int sup = fa8_supported(p->seqlen, p->head_dim, p->v_layout);
   if (sup != FA8_OK) return sup;
@@ -133,6 +135,9 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   args.o_scale = p->o_scale;
   args.status = p->status_word;
   args.lse = p->softmax_lse;
+  args.descale_q = p->descale_q;
+  args.descale_k = p->descale_k;
+  args.descale_v = p->descale_v;
   args.heads = p->heads;
   args.heads_kv = heads_kv;
   args.softmax_scale = p->softmax_scale;
@@ -145,6 +150,22 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
                                   static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess) {
     set_detail("kernel launch", cudaGetErrorString(e));
+    return FA8_ERR_CUDA;
+  }
+  return FA8_OK;
+}
+
+int fa8_quantize_e4m3(const void* src, int32_t src_dtype, void* dst, int64_t n, float* amax,
+                      float* descale, void* cuda_stream) {
+  g_detail[0] = '\0';
+  if (!src || !dst || !amax || n <= 0) return FA8_ERR_BAD_ARG;
+  if (src_dtype != FA8_DTYPE_FP16 && src_dtype != FA8_DTYPE_BF16) return FA8_ERR_BAD_ARG;
+  if (!aligned16(src) || !aligned16(dst)) return FA8_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(amax) & 3u) || (reinterpret_cast<uintptr_t>(descale) & 3u)) return FA8_ERR_BAD_ARG;
+  cudaError_t e = fa8::launch_quantize(src, src_dtype == FA8_DTYPE_BF16, dst, n, amax, descale,
+                                       static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) {
+    set_detail("quantize launch", cudaGetErrorString(e));
     return FA8_ERR_CUDA;
   }
   return FA8_OK;

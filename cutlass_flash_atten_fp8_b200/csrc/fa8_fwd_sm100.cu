@@ -635,7 +635,14 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t t_sb = tmem_base + lane_sel + i * kBlockN + h * kSubN;   // my S buffer
     const uint32_t t_o = tmem_base + lane_sel + kTmemO + i * D;
-    const float c = args.scale_log2;
+    // Per-tensor descales that live on the device (written by the quantisation pre-pass)
+    // fold into the softmax scale (Q, K) and the output scale (V).
+    float qk_descale = 1.f, o_scale = args.o_scale;
+    if (args.descale_q != nullptr) qk_descale *= __ldg(args.descale_q);
+    if (args.descale_k != nullptr) qk_descale *= __ldg(args.descale_k);
+    if (args.descale_v != nullptr) o_scale *= __ldg(args.descale_v);
+    const float c = args.scale_log2 * qk_descale;
+    const float sm_scale = args.softmax_scale * qk_descale;
     RowGroupShared& grp = groups[i * 4 + quarter];
     // Running phase counts of the barriers this warp waits on.
     uint32_t own_cnt = 0;        // sub-blocks taken from my S buffer: s_full[i][h] phases consumed
@@ -764,9 +771,9 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             l_tot += (mp == -INFINITY) ? 0.f : lp * ex2_approx((mp - m_fin) * c);
           }
         }
-        const float inv = ((l_tot == 0.f || l_tot != l_tot) ? 1.f : 1.f / l_tot) * args.o_scale;
+        const float inv = ((l_tot == 0.f || l_tot != l_tot) ? 1.f : 1.f / l_tot) * o_scale;
         if (args.lse != nullptr && h == 0 && q_row < seqlen)    // log(sum exp(scale*s)) = scale*m + log(l)
-          args.lse[static_cast<size_t>(w.bh) * seqlen + q_row] = m_fin * args.softmax_scale + __logf(l_tot);
+          args.lse[static_cast<size_t>(w.bh) * seqlen + q_row] = m_fin * sm_scale + __logf(l_tot);
         __half* o_row = args.o + (static_cast<size_t>(w.bh) * seqlen + q_row) * D + h * (D / 2);
 #pragma unroll
         for (int q = 0; q < D / 64; ++q) {

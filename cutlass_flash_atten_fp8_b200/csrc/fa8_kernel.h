@@ -5,6 +5,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdint>
+
 namespace fa8 {
 
 // By-value kernel arguments.  Plays the role of the reference's
@@ -19,6 +21,9 @@ struct KernelArgs {
   int n_units;                    // work units of the persistent grid (see get_item)
   float scale_log2;               // softmax_scale * log2(e)
   float o_scale;                  // multiplies O/l (1 = reference behaviour)
+  const float* descale_q;         // optional device scalars: softmax scale *= dq*dk, O *= dv
+  const float* descale_k;
+  const float* descale_v;
   float* lse;                     // optional [batch*heads, seqlen] fp32: log-sum-exp of the scaled scores
   float softmax_scale;            // as given by the caller (natural-log units, for lse)
   int* status;                    // optional device word; non-zero after a bounded wait expired
@@ -34,5 +39,10 @@ cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, const CUtensor
 
 // One warp waits (bounded by limit_ns) on a barrier that never completes; see fa8_selftest_expired_wait.
 cudaError_t launch_expired_wait(int* status, unsigned long long limit_ns, cudaStream_t stream);
+
+// Per-tensor amax quantisation fp16/bf16 -> e4m3 (fa8_quant.cu): *amax = max|src|,
+// dst = e4m3(src * 448 / amax), *descale = amax / 448 (descale may be null).
+cudaError_t launch_quantize(const void* src, bool bf16, void* dst, int64_t n, float* amax, float* descale,
+                            cudaStream_t stream);
 
 }  // namespace fa8

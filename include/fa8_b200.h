@@ -70,6 +70,11 @@ typedef struct fa8_fwd_params {
                            h / (heads / heads_kv).  K and V are then [batch, heads_kv, ...].  The
                            reference reserves k_head / h_h_k_ratio for this (csrc/flash.h:36-45) but
                            its kernel ignores them (csrc/flash_attention.cu:364-379). */
+  const float* descale_q; /* optional device floats: x_true = descale * x_e4m3 per tensor.  When given, */
+  const float* descale_k; /* the kernel multiplies softmax_scale by descale_q * descale_k and O by     */
+  const float* descale_v; /* descale_v itself, so the outputs of fa8_quantize_e4m3 can be used without */
+                          /* a device-to-host round trip.  The reference has no descale arguments        */
+                          /* (include/attention_api.h:10-11).                                            */
 } fa8_fwd_params;
 
 /* Enqueues the forward on `cuda_stream` (a cudaStream_t; NULL = default stream)
@@ -82,6 +87,18 @@ int fa8_fwd(const fa8_fwd_params* params, void* cuda_stream);
  * Replaces the reference's cudaDeviceSynchronize + CUDA_ERROR_CHECK
  * (csrc/flash_attention.cu:663-665). */
 int fa8_check_status(const int32_t* status_word, void* cuda_stream, int32_t* code_out);
+
+#define FA8_DTYPE_FP16 0
+#define FA8_DTYPE_BF16 1
+
+/* Per-tensor quantisation of `n` contiguous fp16 / bf16 values to e4m3, enqueued on
+ * `cuda_stream`: *amax = max |src|, dst = e4m3(src * 448 / amax) (round-to-nearest-even,
+ * saturating), *descale = amax / 448 (descale may be NULL).  src and dst 16-byte aligned
+ * device memory, amax and descale device floats.  This is the step the reference's callers do
+ * with torch before the operator (test.py:12-23, 68-70: cast to float8_e4m3fn); here it is two
+ * HBM-bound kernels (5 bytes of traffic per element). */
+int fa8_quantize_e4m3(const void* src, int32_t src_dtype, void* dst, int64_t n, float* amax,
+                      float* descale, void* cuda_stream);
 
 /* Failure-detection self-test (no counterpart in the reference, whose only error path is
  * exit(), include/attention_api.cuh:20-29): enqueues a one-warp kernel that waits on a barrier
@@ -102,8 +119,8 @@ const char* fa8_error_string(int code);
 /* Text of the last CUDA failure seen by the calling thread (empty string if none). */
 const char* fa8_last_error_detail(void);
 
-/* ABI version of this header: major*100 + minor (101 added softmax_lse, 102 heads_kv, both at the
- * end of fa8_fwd_params). */
+/* ABI version of this header: major*100 + minor (101 added softmax_lse, 102 heads_kv, 103 the
+ * descale pointers, all at the end of fa8_fwd_params, and fa8_quantize_e4m3). */
 int fa8_version(void);
 
 #ifdef __cplusplus
