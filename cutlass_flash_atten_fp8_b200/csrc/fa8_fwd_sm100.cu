@@ -680,7 +680,15 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           uint32_t pk[16];
           float bsum = 0.f;
           // Fast path: one pass, exponentials against the maximum known so far.
-          if (have_m) bsum = softmax_pass<true>(t_sb, lim, ek, pk);
+          if (have_m) {
+            if (kCausal && __all_sync(0xffffffffu, lim <= 0)) {
+              // Every row of this warp lies above the diagonal of this sub-block: P = 0.
+#pragma unroll
+              for (int e = 0; e < 16; ++e) pk[e] = 0u;
+            } else {
+              bsum = softmax_pass<true>(t_sb, lim, ek, pk);
+            }
+          }
           // P(sb) may be handed over only after the partner has handed over P(sb-1): from
           // then on nobody else can raise the maximum before PV(sb) is issued.
           if (sb > 0)
