@@ -18,6 +18,8 @@ FA8_ERR_DEVICE_TIMEOUT = -4
 
 FA8_V_TRANSPOSED = 0
 FA8_V_NATURAL = 1
+FA8_FP8_E4M3 = 0
+FA8_FP8_E5M2 = 1
 FA8_DTYPE_FP16 = 0
 FA8_DTYPE_BF16 = 1
 
@@ -36,6 +38,7 @@ class Fa8FwdParams(ctypes.Structure):
         ("v_layout", ctypes.c_int32), ("o_scale", ctypes.c_float), ("status_word", ctypes.c_void_p),
         ("softmax_lse", ctypes.c_void_p), ("heads_kv", ctypes.c_int32),
         ("descale_q", ctypes.c_void_p), ("descale_k", ctypes.c_void_p), ("descale_v", ctypes.c_void_p),
+        ("fp8_format", ctypes.c_int32),
     ]
 
 

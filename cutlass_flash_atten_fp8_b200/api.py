@@ -62,7 +62,8 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
                                descale_v: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
     """FP8 attention forward.
 
-    q, k: float8_e4m3fn [batch, heads, seqlen, head_dim], CUDA, contiguous.  k and v may have
+    q, k: float8_e4m3fn (or, all three, float8_e5m2: the reference's FP8_SWITCH,
+          csrc/flash_attention.cu:631) [batch, heads, seqlen, head_dim], CUDA, contiguous.  k and v may have
           fewer heads (a divisor of q's): grouped-query attention, query head h reading K/V
           head h // (heads // heads_kv).
     v:    float8_e4m3fn, transposed [batch, heads, head_dim, seqlen] as the reference
@@ -81,9 +82,11 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     _check_input(q, "q")
     _check_input(k, "k")
     _check_input(v, "v")
+    if q.dtype not in (torch.float8_e4m3fn, torch.float8_e5m2):
+        raise RuntimeError(f"q must be float8_e4m3fn (or float8_e5m2), got {q.dtype}")
     for name, t in (("q", q), ("k", k), ("v", v)):
-        if t.dtype != torch.float8_e4m3fn:
-            raise RuntimeError(f"{name} must be float8_e4m3fn, got {t.dtype}")
+        if t.dtype != q.dtype:
+            raise RuntimeError(f"{name} must be {q.dtype} like q (float8_e4m3fn or float8_e5m2), got {t.dtype}")
         if t.dim() != 4:
             raise RuntimeError(f"{name} must have 4 dimensions [batch, heads, seqlen, head_dim]")
         if t.device != q.device:
@@ -119,7 +122,8 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         softmax_lse=(lse.data_ptr() if lse is not None else None), heads_kv=Hk,
         descale_q=(descale_q.data_ptr() if descale_q is not None else None),
         descale_k=(descale_k.data_ptr() if descale_k is not None else None),
-        descale_v=(descale_v.data_ptr() if descale_v is not None else None))
+        descale_v=(descale_v.data_ptr() if descale_v is not None else None),
+        fp8_format=(_lib.FA8_FP8_E5M2 if q.dtype == torch.float8_e5m2 else _lib.FA8_FP8_E4M3))
     with torch.cuda.device(q.device):
         rc = lib.fa8_fwd(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
     if rc != _lib.FA8_OK:

@@ -74,7 +74,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 extern "C" {
 
-int fa8_version(void) { return 103; }
+int fa8_version(void) { return 104; }
 
 const char* fa8_error_string(int code) {
   switch (code) {
@@ -108,6 +108,7 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   if ((reinterpret_cast<uintptr_t>(p->descale_q) | reinterpret_cast<uintptr_t>(p->descale_k) |
        reinterpret_cast<uintptr_t>(p->descale_v)) & 3u) return FA8_ERR_BAD_ARG;
   if (p->v_layout != FA8_V_TRANSPOSED && p->v_layout != FA8_V_NATURAL) return FA8_ERR_BAD_ARG;
+  if (p->fp8_format != FA8_FP8_E4M3 && p->fp8_format != FA8_FP8_E5M2) return FA8_ERR_BAD_ARG;
   int sup = fa8_supported(p->seqlen, p->head_dim, p->v_layout);
   if (sup != FA8_OK) return sup;
   const int64_t bh = static_cast<int64_t>(p->batch) * p->heads;
@@ -146,7 +147,8 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   const int64_t per_slice = p->is_causal ? (args.n_pairs + 1) / 2 : args.n_pairs;
   if (bh * per_slice > 0x7fffffff) return FA8_ERR_UNSUPPORTED;
   args.n_units = static_cast<int>(bh * per_slice);
-  cudaError_t e = fa8::launch_fwd(p->head_dim, p->is_causal != 0, p->v_layout == FA8_V_NATURAL, tq, tk, tv, args,
+  cudaError_t e = fa8::launch_fwd(p->head_dim, p->is_causal != 0, p->v_layout == FA8_V_NATURAL,
+                                  p->fp8_format == FA8_FP8_E5M2, tq, tk, tv, args,
                                   static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess) {
     set_detail("kernel launch", cudaGetErrorString(e));

@@ -94,9 +94,11 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t sbo_b
          (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) |
          (static_cast<uint64_t>(layout_type) << 61);
 }
-// kind::f8f6f4 instruction descriptor: e4m3 x e4m3 -> f32, both operands K-major.
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
-  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+// kind::f8f6f4 instruction descriptor: fp8 x fp8 -> f32, both operands K-major; `fmt` is the
+// element format of A and B alike (0 = e4m3, 1 = e5m2; bits 7-9 and 10-12).
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, uint32_t fmt = 0) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 struct WaitCtx {
@@ -138,14 +140,25 @@ __device__ __forceinline__ bool wait_bounded(const WaitCtx& w, uint32_t bar, uin
 // path's clamp at 2^8) before the row maximum is raised.
 constexpr float kLazyLimit = 128.f;
 
-// Four fp32 -> four e4m3 in one word (ascending index = ascending byte).
-__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+// Four fp32 -> four fp8 (e4m3, or e5m2 when the inputs are e5m2, as the reference does with
+// its Element type, csrc/flash_attention.cu:163-179) in one word, ascending index = ascending
+// byte; round-to-nearest-even, saturating.
+template <bool kE5M2>
+__device__ __forceinline__ uint32_t pack4_fp8(float a, float b, float c, float d) {
   uint32_t r;
-  asm("{\n\t.reg .b16 lo, hi;\n\t"
-      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
-      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
-      "mov.b32 %0, {lo, hi};\n\t}"
-      : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+  if (kE5M2) {
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "cvt.rn.satfinite.e5m2x2.f32 lo, %2, %1;\n\t"
+        "cvt.rn.satfinite.e5m2x2.f32 hi, %4, %3;\n\t"
+        "mov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+  } else {
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+        "mov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+  }
   return r;
 }
 
@@ -177,7 +190,7 @@ struct ExpConsts {
   }
 };
 
-template <bool kAllowFma>
+template <bool kAllowFma, bool kE5M2>
 __device__ __forceinline__ void softmax_chunk(uint32_t t_cols, int lim, const ExpConsts& k,
                                               uint32_t* pk, f32x2_t (&ls)[2]) {
   const f32x2_t k128 = pack2(128.f, 128.f);
@@ -221,17 +234,17 @@ __device__ __forceinline__ void softmax_chunk(uint32_t t_cols, int lim, const Ex
       }
       ls[u >> 1] = add2(ls[u >> 1], pack2(p[u], p[u + 1]));
     }
-    pk[e / 4] = pack4_e4m3(p[0], p[1], p[2], p[3]);
+    pk[e / 4] = pack4_fp8<kE5M2>(p[0], p[1], p[2], p[3]);
   }
 }
 
 // P of one 64-key sub-block of this thread's row -> pk[16]; returns the fp32 row sum.
-template <bool kAllowFma>
+template <bool kAllowFma, bool kE5M2>
 __device__ __forceinline__ float softmax_pass(uint32_t t_sb, int lim, const ExpConsts& k,
                                               uint32_t (&pk)[16]) {
   f32x2_t ls[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
-  softmax_chunk<kAllowFma>(t_sb, lim, k, pk, ls);
-  softmax_chunk<kAllowFma>(t_sb + 32, lim - 32, k, pk + 8, ls);
+  softmax_chunk<kAllowFma, kE5M2>(t_sb, lim, k, pk, ls);
+  softmax_chunk<kAllowFma, kE5M2>(t_sb + 32, lim - 32, k, pk + 8, ls);
   float a0, a1, a2, a3;
   unpack2(ls[0], a0, a1);
   unpack2(ls[1], a2, a3);
@@ -334,7 +347,7 @@ __device__ __forceinline__ bool get_item(const KernelArgs& a, int unit, int k, I
 
 }  // namespace
 
-template <int D, bool kCausal, bool kVNatural>
+template <int D, bool kCausal, bool kVNatural, bool kE5M2>
 __global__ void __launch_bounds__(kThreads, 1)
 fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const KernelArgs args) {
@@ -498,9 +511,10 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // committed it (kv_empty counts two arrivals).
     if (elect_one()) {
       const int i = warp - kMmaWarp0;
-      constexpr uint32_t kIdescQK = umma_idesc(kTileM, kSubN);
+      constexpr uint32_t kFmt = kE5M2 ? 1u : 0u;
+      constexpr uint32_t kIdescQK = umma_idesc(kTileM, kSubN, kFmt);
       // V in its natural [keys, head_dim] layout is an MN-major B operand (bit 16).
-      constexpr uint32_t kIdescPV = umma_idesc(kTileM, D) | (kVNatural ? (1u << 16) : 0u);
+      constexpr uint32_t kIdescPV = umma_idesc(kTileM, D, kFmt) | (kVNatural ? (1u << 16) : 0u);
       constexpr uint32_t kSlotMask = C::kSlots - 1;
       static_assert((C::kSlots & (C::kSlots - 1)) == 0, "ring size must be a power of two");
       constexpr int kSlotShift = (C::kSlots == 8) ? 3 : 4;
@@ -686,7 +700,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
               for (int e = 0; e < 16; ++e) pk[e] = 0u;
             } else {
-              bsum = softmax_pass<true>(t_sb, lim, ek, pk);
+              bsum = softmax_pass<true, kE5M2>(t_sb, lim, ek, pk);
             }
           }
           // P(sb) may be handed over only after the partner has handed over P(sb-1): from
@@ -713,7 +727,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 version = v;
                 have_m = true;
                 ek.set_max(-m * c);
-                bsum = softmax_pass<false>(t_sb, lim, ek, pk);
+                bsum = softmax_pass<false, kE5M2>(t_sb, lim, ek, pk);
               }
               exact = __any_sync(0xffffffffu, !(bsum <= kLazyLimit));
             }
@@ -741,7 +755,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               __syncwarp();
               if (lane == 0) grp.version = version;
               ek.set_max((m == -INFINITY) ? 0.f : -m * c);
-              bsum = softmax_pass<false>(t_sb, lim, ek, pk);
+              bsum = softmax_pass<false, kE5M2>(t_sb, lim, ek, pk);
             }
           }
           l += bsum;
@@ -843,10 +857,10 @@ cudaError_t launch_expired_wait(int* status, unsigned long long limit_ns, cudaSt
 template <int D>
 static constexpr int smem_bytes_for() { return Cfg<D>::kSmemBytes; }
 
-template <int D, bool kCausal, bool kVNatural>
+template <int D, bool kCausal, bool kVNatural, bool kE5M2>
 static cudaError_t launch_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                               const KernelArgs& args, cudaStream_t stream) {
-  auto kernel = &fa8_fwd_kernel<D, kCausal, kVNatural>;
+  auto kernel = &fa8_fwd_kernel<D, kCausal, kVNatural, kE5M2>;
   constexpr int smem = Cfg<D>::kSmemBytes;
   static bool attr_set[64] = {};
   static int sm_count[64] = {};
@@ -880,19 +894,28 @@ static cudaError_t launch_one(const CUtensorMap& tq, const CUtensorMap& tk, cons
   return cudaGetLastError();
 }
 
-cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, const CUtensorMap& tq,
+template <int D, bool kCausal>
+static cudaError_t launch_layout(bool v_natural, bool e5m2, const CUtensorMap& tq, const CUtensorMap& tk,
+                                 const CUtensorMap& tv, const KernelArgs& args, cudaStream_t stream) {
+  if (v_natural) {
+    return e5m2 ? launch_one<D, kCausal, true, true>(tq, tk, tv, args, stream)
+                : launch_one<D, kCausal, true, false>(tq, tk, tv, args, stream);
+  }
+  return e5m2 ? launch_one<D, kCausal, false, true>(tq, tk, tv, args, stream)
+              : launch_one<D, kCausal, false, false>(tq, tk, tv, args, stream);
+}
+
+cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, const CUtensorMap& tq,
                        const CUtensorMap& tk, const CUtensorMap& tv, const KernelArgs& args,
                        cudaStream_t stream) {
-#define FA8_LAUNCH(DD, CC, VV) return launch_one<DD, CC, VV>(tq, tk, tv, args, stream)
   if (head_dim == 128) {
-    if (causal) { if (v_natural) FA8_LAUNCH(128, true, true); else FA8_LAUNCH(128, true, false); }
-    else { if (v_natural) FA8_LAUNCH(128, false, true); else FA8_LAUNCH(128, false, false); }
+    return causal ? launch_layout<128, true>(v_natural, e5m2, tq, tk, tv, args, stream)
+                  : launch_layout<128, false>(v_natural, e5m2, tq, tk, tv, args, stream);
   }
   if (head_dim == 64) {
-    if (causal) { if (v_natural) FA8_LAUNCH(64, true, true); else FA8_LAUNCH(64, true, false); }
-    else { if (v_natural) FA8_LAUNCH(64, false, true); else FA8_LAUNCH(64, false, false); }
+    return causal ? launch_layout<64, true>(v_natural, e5m2, tq, tk, tv, args, stream)
+                  : launch_layout<64, false>(v_natural, e5m2, tq, tk, tv, args, stream);
   }
-#undef FA8_LAUNCH
   return cudaErrorInvalidValue;
 }
 

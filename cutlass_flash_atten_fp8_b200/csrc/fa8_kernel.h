@@ -33,7 +33,8 @@ struct KernelArgs {
 // Launches the persistent forward kernel for head_dim in {64,128}.
 // v_natural: V is [slices, seqlen, head_dim] (tv describes it like K) instead of the
 // reference's transposed [slices, head_dim, seqlen].
-cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, const CUtensorMap& tq,
+// e5m2: Q, K, V (and P) are e5m2 instead of e4m3.
+cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, const CUtensorMap& tq,
                        const CUtensorMap& tk, const CUtensorMap& tv, const KernelArgs& args,
                        cudaStream_t stream);
 

@@ -41,6 +41,9 @@ extern "C" {
 #define FA8_V_TRANSPOSED 0 /* [batch, heads, head_dim, seqlen], seqlen contiguous (reference layout) */
 #define FA8_V_NATURAL 1    /* [batch, heads, seqlen, head_dim], head_dim contiguous */
 
+#define FA8_FP8_E4M3 0
+#define FA8_FP8_E5M2 1
+
 /* Arguments of one forward call; mirrors the live fields of the reference's
  * Flash_fwd_params (csrc/flash.h:6-61).  All tensors are contiguous device
  * memory, 16-byte aligned. */
@@ -75,6 +78,9 @@ typedef struct fa8_fwd_params {
   const float* descale_v; /* descale_v itself, so the outputs of fa8_quantize_e4m3 can be used without */
                           /* a device-to-host round trip.  The reference has no descale arguments        */
                           /* (include/attention_api.h:10-11).                                            */
+  int32_t fp8_format;   /* FA8_FP8_E4M3 (0) or FA8_FP8_E5M2: element format of Q, K and V alike; P is
+                           re-quantised to the same format.  The reference switches on the input dtype
+                           the same way (FP8_SWITCH, csrc/flash_attention.cu:308,631). */
 } fa8_fwd_params;
 
 /* Enqueues the forward on `cuda_stream` (a cudaStream_t; NULL = default stream)
@@ -120,7 +126,8 @@ const char* fa8_error_string(int code);
 const char* fa8_last_error_detail(void);
 
 /* ABI version of this header: major*100 + minor (101 added softmax_lse, 102 heads_kv, 103 the
- * descale pointers, all at the end of fa8_fwd_params, and fa8_quantize_e4m3). */
+ * descale pointers and fa8_quantize_e4m3, 104 fp8_format; new fields go at the end of
+ * fa8_fwd_params). */
 int fa8_version(void);
 
 #ifdef __cplusplus

@@ -92,6 +92,46 @@ def e4m3_encode(x: np.ndarray) -> np.ndarray:
     return (bits | sign).astype(np.uint8)
 
 
+E5M2_MAX = 57344.0
+
+
+def _e5m2_decode_table() -> np.ndarray:
+    t = np.zeros(256, dtype=np.float32)
+    for b in range(256):
+        sign = -1.0 if (b & 0x80) else 1.0
+        e = (b >> 2) & 0x1F
+        m = b & 0x3
+        if e == 0x1F:
+            v = float("inf") if m == 0 else float("nan")
+        elif e == 0:
+            v = (m / 4.0) * 2.0 ** (-14)
+        else:
+            v = (1.0 + m / 4.0) * 2.0 ** (e - 15)
+        t[b] = sign * v
+    return t
+
+
+_DECODE_E5M2 = _e5m2_decode_table()
+
+
+def e5m2_decode(bits: np.ndarray) -> np.ndarray:
+    """uint8 e5m2 bit patterns -> float32."""
+    return _DECODE_E5M2[np.asarray(bits, dtype=np.uint8)]
+
+
+def e5m2_round(x: np.ndarray) -> np.ndarray:
+    """float32 -> nearest e5m2 VALUE (as float32), round-to-nearest-even, saturating to +-57344
+    (cvt.rn.satfinite.e5m2x2.f32 semantics); used for P of the e5m2 path."""
+    x = np.asarray(x, dtype=np.float32)
+    a = np.minimum(np.abs(x).astype(np.float64), E5M2_MAX)
+    with np.errstate(divide="ignore"):
+        e = np.floor(np.log2(np.where(a > 0, a, 1.0)))
+    e = np.clip(e, -14, 15)
+    step = 2.0 ** (e - 2)
+    val = np.minimum(np.rint(a / step) * step, E5M2_MAX)
+    return (np.sign(x) * val).astype(np.float32)
+
+
 def _as_f32(x8) -> torch.Tensor:
     """Accepts uint8 bit patterns (numpy / torch) or a float8_e4m3fn tensor."""
     if isinstance(x8, np.ndarray):
@@ -143,9 +183,11 @@ def attention_reference_fp16(q8, k8, v8, causal: bool, softmax_scale: float) -> 
 
 def attention_quantised_p(q8, k8, v8, causal: bool, softmax_scale: float, block_n: int = 128,
                           o_scale: float = 1.0, lazy: bool = False, lazy_limit: float = 256.0,
-                          lazy_rows: int = 32) -> torch.Tensor:
-    """Model of an FP8 kernel (see module docstring).  Raw e4m3 values are used
-    as they are (no descale), like the reference kernel.  Returns fp32 [B,H,S,D]
+                          lazy_rows: int = 32, p_format: str = "e4m3") -> torch.Tensor:
+    """Model of an FP8 kernel (see module docstring).  Raw fp8 values are used
+    as they are (no descale), like the reference kernel; P is rounded to `p_format`
+    ("e4m3", or "e5m2" when the inputs are e5m2, csrc/flash_attention.cu:163-179,631).
+    Returns fp32 [B,H,S,D]
     *before* any rounding of O.
 
     lazy=False is the reference's rule: the running maximum m follows every block
@@ -184,7 +226,8 @@ def attention_quantised_p(q8, k8, v8, causal: bool, softmax_scale: float, block_
                 m_eff = torch.where(torch.isinf(m_new), torch.zeros_like(m_new), m_new)
                 p = torch.exp(s * softmax_scale - (m_eff * softmax_scale).unsqueeze(1))
                 l = l * alpha + p.sum(dim=1)
-                p8 = torch.from_numpy(e4m3_decode(e4m3_encode(p.numpy())))
+                p8 = torch.from_numpy(e5m2_round(p.numpy()) if p_format == "e5m2"
+                                      else e4m3_decode(e4m3_encode(p.numpy())))
                 acc = acc * alpha.unsqueeze(1) + p8 @ v[b, h, n0:n1]
                 m = m_new
             inv = torch.where((l == 0) | torch.isnan(l), torch.ones_like(l), 1.0 / l)

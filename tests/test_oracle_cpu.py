@@ -38,6 +38,21 @@ def test_e4m3_codec_matches_torch():
     assert list(e4m3_encode(np.array([1e9, -1e9, 449, 464, np.nan], dtype=np.float32))) == [126, 254, 126, 126, 127]
 
 
+def test_e5m2_codec_matches_torch():
+    from oracle.attention_oracle import e5m2_decode, e5m2_round
+    bits = np.arange(256, dtype=np.uint8)
+    t = torch.from_numpy(bits).view(torch.float8_e5m2).float().numpy()
+    d = e5m2_decode(bits)
+    assert np.array_equal(np.isnan(t), np.isnan(d))
+    assert np.array_equal(t[~np.isnan(t)], d[~np.isnan(d)])
+    rng = np.random.default_rng(1)
+    x = np.concatenate([rng.standard_normal(50000).astype(np.float32) * s for s in (1e-5, 1e-3, 0.1, 1, 100, 3e4)])
+    x = x[np.abs(x) <= 57344]
+    theirs = torch.from_numpy(x).to(torch.float8_e5m2).float().numpy()
+    assert np.array_equal(e5m2_round(x), theirs)
+    assert list(e5m2_round(np.array([1e9, -1e9, 60000.0], dtype=np.float32))) == [57344.0, -57344.0, 57344.0]
+
+
 def test_restatement_is_bit_exact_on_reference_fixtures(golden_dir):
     for f in _golden(golden_dir):
         g = np.load(f)

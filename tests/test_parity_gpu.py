@@ -150,6 +150,28 @@ def test_grouped_query_attention(Hk, causal):
         flash_attention_v2_cutlass(q8.to(d), rand8(B, 3, S, D, seed=73).to(d), v8.to(d), causal, scale)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_e5m2_inputs(D, causal):
+    """Q, K, V in e5m2 (the reference's other element type, csrc/flash_attention.cu:308,631); P is
+    rounded to e5m2 too, which has one mantissa bit less: tolerance against fp32 is 6e-2."""
+    E5 = torch.float8_e5m2
+    B, H, S = 2, 2, 576
+    g = torch.Generator().manual_seed(55 + D)
+    q8, k8, v8 = (torch.randn(B, H, S, D, generator=g).to(E5) for _ in range(3))
+    scale = 1 / math.sqrt(D)
+    d = dev()
+    out = flash_attention_v2_cutlass(q8.to(d), k8.to(d), v8.to(d).transpose(2, 3).contiguous(), causal, scale)[0]
+    check_status(d)
+    ref = attention_fp32(q8, k8, v8, causal, scale)
+    m = error_metrics(out, ref)
+    assert m["rel_l2"] <= 6e-2 and m["max_abs"] <= 0.1 * m["max_ref"], m
+    model = attention_quantised_p(q8, k8, v8, causal, scale, p_format="e5m2", **KERNEL_MODEL)
+    assert error_metrics(out, model)["rel_l2"] <= REL_L2_MODEL
+    with pytest.raises(RuntimeError, match="like q"):
+        flash_attention_v2_cutlass(q8.to(d), k8.to(d).to(torch.float8_e4m3fn), v8.to(d), causal, scale)
+
+
 def test_known_answers():
     S, D = 512, 128
     q8, k8 = rand8(1, 2, S, D, seed=1), rand8(1, 2, S, D, seed=2)
