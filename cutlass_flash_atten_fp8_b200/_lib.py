@@ -38,7 +38,7 @@ class Fa8FwdParams(ctypes.Structure):
         ("v_layout", ctypes.c_int32), ("o_scale", ctypes.c_float), ("status_word", ctypes.c_void_p),
         ("softmax_lse", ctypes.c_void_p), ("heads_kv", ctypes.c_int32),
         ("descale_q", ctypes.c_void_p), ("descale_k", ctypes.c_void_p), ("descale_v", ctypes.c_void_p),
-        ("fp8_format", ctypes.c_int32),
+        ("fp8_format", ctypes.c_int32), ("seqlen_k", ctypes.c_int32),
     ]
 
 

@@ -65,7 +65,8 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     q, k: float8_e4m3fn (or, all three, float8_e5m2: the reference's FP8_SWITCH,
           csrc/flash_attention.cu:631) [batch, heads, seqlen, head_dim], CUDA, contiguous.  k and v may have
           fewer heads (a divisor of q's): grouped-query attention, query head h reading K/V
-          head h // (heads // heads_kv).
+          head h // (heads // heads_kv); their sequence length may differ from q's (the causal
+          mask stays top-left aligned: key index <= query index).
     v:    float8_e4m3fn, transposed [batch, heads, head_dim, seqlen] as the reference
           requires (test.py:71), or [batch, heads, seqlen, head_dim] with
           v_layout="natural".
@@ -92,14 +93,14 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         if t.device != q.device:
             raise RuntimeError("q, k and v must be on the same device")
     B, H, S, D = q.shape
-    Hk = k.shape[1]
-    if tuple(k.shape) != (B, Hk, S, D) or Hk < 1 or H % Hk != 0:
+    Hk, Sk = k.shape[1], k.shape[2]
+    if tuple(k.shape) != (B, Hk, Sk, D) or Hk < 1 or H % Hk != 0:
         raise RuntimeError(f"k must be [batch, heads_kv, seqlen, head_dim] with heads_kv dividing {H}; "
                            f"q is {tuple(q.shape)}, k is {tuple(k.shape)}")
     if v_layout == "transposed":
-        want_v, layout = (B, Hk, D, S), _lib.FA8_V_TRANSPOSED
+        want_v, layout = (B, Hk, D, Sk), _lib.FA8_V_TRANSPOSED
     elif v_layout == "natural":
-        want_v, layout = (B, Hk, S, D), _lib.FA8_V_NATURAL
+        want_v, layout = (B, Hk, Sk, D), _lib.FA8_V_NATURAL
     else:
         raise RuntimeError("v_layout must be 'transposed' or 'natural'")
     if tuple(v.shape) != want_v:
@@ -123,7 +124,8 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         descale_q=(descale_q.data_ptr() if descale_q is not None else None),
         descale_k=(descale_k.data_ptr() if descale_k is not None else None),
         descale_v=(descale_v.data_ptr() if descale_v is not None else None),
-        fp8_format=(_lib.FA8_FP8_E5M2 if q.dtype == torch.float8_e5m2 else _lib.FA8_FP8_E4M3))
+        fp8_format=(_lib.FA8_FP8_E5M2 if q.dtype == torch.float8_e5m2 else _lib.FA8_FP8_E4M3),
+        seqlen_k=Sk)
     with torch.cuda.device(q.device):
         rc = lib.fa8_fwd(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
     if rc != _lib.FA8_OK:

@@ -74,7 +74,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 extern "C" {
 
-int fa8_version(void) { return 104; }
+int fa8_version(void) { return 105; }
 
 const char* fa8_error_string(int code) {
   switch (code) {
@@ -116,22 +116,27 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   if (heads_kv > p->heads || p->heads % heads_kv != 0) return FA8_ERR_BAD_ARG;
   const int64_t bh_kv = static_cast<int64_t>(p->batch) * heads_kv;
 
+  const int32_t seqlen_k = p->seqlen_k > 0 ? p->seqlen_k : p->seqlen;
+  if (p->seqlen_k < 0) return FA8_ERR_BAD_ARG;
+  if (fa8_supported(seqlen_k, p->head_dim, p->v_layout) != FA8_OK) return FA8_ERR_UNSUPPORTED;
   const uint64_t S = static_cast<uint64_t>(p->seqlen), D = static_cast<uint64_t>(p->head_dim);
+  const uint64_t Sk = static_cast<uint64_t>(seqlen_k);
   const CUtensorMapSwizzle sw_qk = (p->head_dim == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap tq, tk, tv;
   if (!make_map_3d(&tq, p->q, D, S, bh, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
-  if (!make_map_3d(&tk, p->k, D, S, bh_kv, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
+  if (!make_map_3d(&tk, p->k, D, Sk, bh_kv, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
   if (p->v_layout == FA8_V_NATURAL) {
     // V: [bh, S, D] like K; a tile is 128 key rows of D bytes.
-    if (!make_map_3d(&tv, p->v, D, S, bh_kv, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
+    if (!make_map_3d(&tv, p->v, D, Sk, bh_kv, static_cast<uint32_t>(D), 128, sw_qk)) return FA8_ERR_CUDA;
   } else {
     // V^T: [bh, D, S]; a tile is D rows of 128 consecutive key positions.
-    if (!make_map_3d(&tv, p->v, S, D, bh_kv, 128, static_cast<uint32_t>(D), CU_TENSOR_MAP_SWIZZLE_128B)) return FA8_ERR_CUDA;
+    if (!make_map_3d(&tv, p->v, Sk, D, bh_kv, 128, static_cast<uint32_t>(D), CU_TENSOR_MAP_SWIZZLE_128B)) return FA8_ERR_CUDA;
   }
 
   fa8::KernelArgs args;
   args.o = static_cast<__half*>(p->o);
   args.seqlen = p->seqlen;
+  args.seqlen_k = seqlen_k;
   args.scale_log2 = p->softmax_scale * 1.4426950408889634f;
   args.o_scale = p->o_scale;
   args.status = p->status_word;

@@ -335,7 +335,9 @@ __device__ __forceinline__ bool get_item(const KernelArgs& a, int unit, int k, I
     const int r0 = it.row0 + i * kTileM;
     int n = 0;
     if (r0 < a.seqlen) {
-      const int col_end = kCausal ? min(r0 + kTileM, a.seqlen) : a.seqlen;   // one past the last visible key
+      // one past the last visible key; the causal mask is aligned top-left (key <= query row),
+      // like the reference's (csrc/flash_attention.cu:24-71, test.py:25-33)
+      const int col_end = kCausal ? min(r0 + kTileM, a.seqlen_k) : a.seqlen_k;
       n = (col_end + kSubN - 1) / kSubN;
     }
     it.nsb_t[i] = n;
@@ -676,7 +678,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int tile_nsb = w.nsb_t[i];
         if (tile_nsb == 0) continue;
         const int q_row = w.row0 + i * kTileM + row;       // global query row, may be >= seqlen
-        const int col_lim = kCausal ? min(seqlen, q_row + 1) : seqlen;   // keys this row may see
+        const int col_lim = kCausal ? min(args.seqlen_k, q_row + 1) : args.seqlen_k;   // keys this row may see
         const uint32_t ib = items & 1u;
         // m is the row maximum the exponentials are taken against, shared by the two warps
         // of the row group through grp.m / grp.version: exact after sub-block 0, then raised

@@ -14,7 +14,8 @@ namespace fa8 {
 // and strides travel in the three TMA descriptors instead.
 struct KernelArgs {
   __half* o;                      // [batch*heads, seqlen, head_dim] fp16
-  int seqlen;                     // queries == keys
+  int seqlen;                     // query rows per slice
+  int seqlen_k;                   // key/value rows per slice
   int heads;                      // query heads per batch entry
   int heads_kv;                   // K/V heads per batch entry (divides heads)
   int n_pairs;                    // ceil(seqlen / 256): pairs of 128-row query tiles per slice

@@ -54,7 +54,7 @@ typedef struct fa8_fwd_params {
   void* o;         /* fp16 [batch, heads, seqlen, head_dim], written by the call */
   int32_t batch;
   int32_t heads;
-  int32_t seqlen;    /* queries and keys alike (the reference has no other case); multiple of 16 */
+  int32_t seqlen;    /* query rows per head (and key rows unless seqlen_k says otherwise); multiple of 16 */
   int32_t head_dim;  /* 64 or 128 */
   float softmax_scale; /* > 0; P = exp(softmax_scale * (S - rowmax)) */
   int32_t is_causal;   /* 0/1; mask is lower-triangular including the diagonal (test.py:25-33) */
@@ -81,6 +81,11 @@ typedef struct fa8_fwd_params {
   int32_t fp8_format;   /* FA8_FP8_E4M3 (0) or FA8_FP8_E5M2: element format of Q, K and V alike; P is
                            re-quantised to the same format.  The reference switches on the input dtype
                            the same way (FP8_SWITCH, csrc/flash_attention.cu:308,631). */
+  int32_t seqlen_k;     /* rows of K and V per head when they differ from `seqlen` (cross attention,
+                           a prompt attending to a longer cache); 0 = seqlen.  Multiple of 16.  The
+                           causal mask stays aligned top-left (key index <= query index), as in the
+                           reference (csrc/flash_attention.cu:24-71); the reference carries q_seqlen and
+                           k_seqlen separately (csrc/flash.h) but its test only runs them equal. */
 } fa8_fwd_params;
 
 /* Enqueues the forward on `cuda_stream` (a cudaStream_t; NULL = default stream)
@@ -126,8 +131,8 @@ const char* fa8_error_string(int code);
 const char* fa8_last_error_detail(void);
 
 /* ABI version of this header: major*100 + minor (101 added softmax_lse, 102 heads_kv, 103 the
- * descale pointers and fa8_quantize_e4m3, 104 fp8_format; new fields go at the end of
- * fa8_fwd_params). */
+ * descale pointers and fa8_quantize_e4m3, 104 fp8_format, 105 seqlen_k; new fields go at
+ * the end of fa8_fwd_params). */
 int fa8_version(void);
 
 #ifdef __cplusplus

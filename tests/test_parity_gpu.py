@@ -172,6 +172,27 @@ def test_e5m2_inputs(D, causal):
         flash_attention_v2_cutlass(q8.to(d), k8.to(d).to(torch.float8_e4m3fn), v8.to(d), causal, scale)
 
 
+@pytest.mark.parametrize("Sq,Sk", [(128, 1024), (1024, 320), (400, 640), (16, 2048)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_different_query_and_key_lengths(Sq, Sk, causal):
+    d = dev()
+    B, H, D = 2, 2, 128
+    q8 = rand8(B, H, Sq, D, seed=Sq)
+    k8, v8 = rand8(B, H, Sk, D, seed=Sk + 1), rand8(B, H, Sk, D, seed=Sk + 2)
+    scale = 1 / math.sqrt(D)
+    out, lse = flash_attention_v2_cutlass(q8.to(d), k8.to(d), v8.to(d), causal, scale, v_layout="natural",
+                                          return_lse=True)
+    check_status(d)
+    s = torch.matmul(q8.float(), k8.float().transpose(2, 3)) * scale
+    if causal:      # top-left aligned: key index <= query index
+        s = s.masked_fill(torch.arange(Sk).unsqueeze(0) > torch.arange(Sq).unsqueeze(1), float("-inf"))
+    ref = torch.softmax(s, dim=-1) @ v8.float()
+    m = error_metrics(out, ref)
+    assert tuple(out.shape) == (B, H, Sq, D)
+    assert m["rel_l2"] <= REL_L2_FP32 and m["max_abs"] <= MAX_ABS_FRAC_FP32 * m["max_ref"], m
+    assert float((lse.cpu() - torch.logsumexp(s, dim=-1)).abs().max()) <= 2e-3
+
+
 def test_known_answers():
     S, D = 512, 128
     q8, k8 = rand8(1, 2, S, D, seed=1), rand8(1, 2, S, D, seed=2)
