@@ -86,13 +86,19 @@ struct Cfg {
   static constexpr uint32_t kQKSbo = 8 * D;                      // bytes between 8-row groups
 };
 
-// Shared-memory matrix descriptor for a K-major swizzled operand tile
-// (rows of `row_bytes` <= 128, eight rows per swizzle atom).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t sbo_bytes,
-                                              uint32_t layout_type) {
-  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) |
-         (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) |
-         (static_cast<uint64_t>(layout_type) << 61);
+// Shared-memory matrix descriptor for a K-major swizzled operand tile (rows of at most 128
+// bytes, eight rows per swizzle atom): start address >> 4 in bits 0-13, leading-dimension
+// offset 1 at bit 16, stride between 8-row groups >> 4 at bit 32, version 1 at bit 46, swizzle
+// mode in bits 61-63.  Kept as two 32-bit words: only the low word (start address) changes
+// from one operand slice to the next.
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
+}
+__device__ __forceinline__ uint32_t umma_desc_hi(uint32_t sbo_bytes, uint32_t layout_type) {
+  return (sbo_bytes >> 4) | (1u << 14) | (layout_type << 29);
+}
+__device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi) {
+  return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 // kind::f8f6f4 instruction descriptor: fp8 x fp8 -> f32, both operands K-major; `fmt` is the
 // element format of A and B alike (0 = e4m3, 1 = e5m2; bits 7-9 and 10-12).
@@ -520,115 +526,133 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       constexpr uint32_t kSlotMask = C::kSlots - 1;
       static_assert((C::kSlots & (C::kSlots - 1)) == 0, "ring size must be a power of two");
       constexpr int kSlotShift = (C::kSlots == 8) ? 3 : 4;
-      bool ok = true;
-      uint32_t kv_base = 0;            // index of the current item's first K/V load (K_0)
-      uint32_t qn = 0;                 // work items of this tile so far
-      uint32_t p_cnt0 = 0, p_cnt1 = 0; // P phases consumed per S buffer
-      const uint32_t t_s = tmem_base + i * kBlockN;
+      constexpr uint32_t kTile16 = C::kTileBytes / 16;     // one tile in descriptor address units
+      // This one thread paces the whole tile, so its instruction count per step is kept low:
+      // descriptors are 32-bit low words (start address in units of 16 bytes; the high word
+      // never changes), barrier addresses and parities are carried, not recomputed.
+      const uint32_t qk_hi = umma_desc_hi(C::kQKSbo, C::kQKLayout);
+      const uint32_t v_hi = kVNatural ? qk_hi : umma_desc_hi(1024u, 2u);
+      const uint32_t q_lo0 = umma_desc_lo(s_q + i * C::kTileBytes);
+      const uint32_t ring_lo = umma_desc_lo(s_ring);
+      const uint32_t t_s0 = tmem_base + i * kBlockN, t_s1 = t_s0 + kSubN;
       const uint32_t t_o = tmem_base + kTmemO + i * D;
-      // Descriptors differ only in the 14-bit start-address field (units of 16 bytes).
-      const uint64_t dq_base = umma_desc(s_q + i * C::kTileBytes, C::kQKSbo, C::kQKLayout);
-      const uint64_t dk_base = umma_desc(s_ring, C::kQKSbo, C::kQKLayout);
-      const uint64_t dv_base = kVNatural ? umma_desc(s_ring, C::kQKSbo, C::kQKLayout) : umma_desc(s_ring, 1024u, 2u);
-      auto slot_of = [&](uint32_t load) { return load & kSlotMask; };
-      auto parity_of = [&](uint32_t load) { return (load >> kSlotShift) & 1u; };
-      // S_i[h] = Q_i K_sb^T for sub-block sb = 2j+h: rows 64h..64h+63 of tile K_j;
-      // D/32 steps of K=32 bytes along the swizzled rows.  Operands are worked out by the
-      // caller before it starts waiting, so that the MMAs go out right after the wait.
-      auto desc_q = [&](uint32_t st) { return dq_base + st * (2 * C::kTileBytes / 16); };
-      auto desc_k = [&](uint32_t load, int h) {
-        return dk_base + (slot_of(load) * C::kTileBytes + h * kSubN * D) / 16;
-      };
+      const uint32_t b_sf0 = bar_s_full(i, 0), b_sf1 = bar_s_full(i, 1);
+      const uint32_t b_pf0 = bar_p_full(i, 0), b_pf1 = bar_p_full(i, 1);
+      const uint32_t b_od = bar_o_done(i), b_ofin = bar_o_final(i), b_ofree = bar_o_free(i);
       // The V^T tile is D rows of 128 key positions (K-major, 128-byte swizzle), of which
-      // sub-block h covers bytes 64h..64h+63 of every row = K-steps 2h and 2h+1.
-      // In the natural layout the tile is 128 key rows of D bytes (swizzled like K): a K-step
-      // of 32 keys is 32 rows further down.
+      // sub-block h covers bytes 64h..64h+63 of every row = K-steps 2h and 2h+1.  In the
+      // natural layout the tile is 128 key rows of D bytes (swizzled like K): a K-step of 32
+      // keys is 32 rows further down.
       constexpr uint32_t kVStep = kVNatural ? (32u * D / 16u) : 2u;   // descriptor units per 32 keys
-      auto desc_v = [&](uint32_t load, int h) {
-        return dv_base + (slot_of(load) * C::kTileBytes) / 16 + 2u * kVStep * h;
-      };
-      auto issue_qk = [&](uint32_t ts, uint64_t dq, uint64_t dk) {
+      constexpr uint32_t kKHalf = kSubN * D / 16;                     // rows 64..127 of a K tile
+      // S_i[h] = Q_i K_sb^T: D/32 steps of K = 32 bytes along the swizzled rows.
+      auto issue_qk = [&](uint32_t ts, uint32_t q_lo, uint32_t k_lo) {
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k) mma_f8_ss(ts, dq + 2u * k, dk + 2u * k, kIdescQK, k > 0);
+        for (int k = 0; k < D / 32; ++k)
+          mma_f8_ss(ts, make_desc(q_lo + 2u * k, qk_hi), make_desc(k_lo + 2u * k, qk_hi), kIdescQK, k > 0);
       };
-      // O_i (+)= P_i(sb) V_sb: P is 128 rows x 64 e4m3 = 16 TMEM columns over S_i[h].
-      auto issue_pv = [&](uint32_t ts, uint64_t dv, bool acc) {
+      // O_i (+)= P_i(sb) V_sb: P is 128 rows x 64 fp8 = 16 TMEM columns over S_i[h].
+      auto issue_pv = [&](uint32_t ts, uint32_t v_lo, bool acc) {
 #pragma unroll
         for (int k = 0; k < kSubN / 32; ++k)
-          mma_f8_ts(t_o, ts + 8u * k, dv + kVStep * k, kIdescPV, (acc || k > 0) ? 1u : 0u);
+          mma_f8_ts(t_o, ts + 8u * k, make_desc(v_lo + kVStep * k, v_hi), kIdescPV, (acc || k > 0) ? 1u : 0u);
       };
+      auto kv_wait = [&](uint32_t load) {
+        const uint32_t slot = load & kSlotMask;
+        return wait_bounded(wctx, b_kv_full + 8u * slot, (load >> kSlotShift) & 1u, 0x200 + slot);
+      };
+      auto kv_release = [&](uint32_t load) { tc_commit(b_kv_empty + 8u * (load & kSlotMask)); };
+      auto kv_lo = [&](uint32_t load) { return ring_lo + (load & kSlotMask) * kTile16; };
+
+      bool ok = true;
+      uint32_t ld = 0;                 // index of the current item's first K/V load (K_0)
+      uint32_t qn = 0;                 // work items of this tile so far
+      uint32_t pp0 = 0, pp1 = 0;       // parity of the next P phase per S buffer
 
       for (int unit = blockIdx.x; unit < args.n_units && ok; unit += gridDim.x) {
         for (int kk = 0; kk < kItemsPerUnit && ok; ++kk) {
           Item w;
           if (!get_item<kCausal>(args, unit, kk, w)) continue;
           const int nsb = (i == 0) ? w.nsb_t[0] : w.nsb_t[1];
-          const uint32_t n_loads = 2u * static_cast<uint32_t>(w.nb);
-          // The item's loads are K_0, V_0, K_1, V_1, ... = kv_base + 0, 1, 2, ...  This thread
-          // waits for each of them once, in order, and hands each back once, in order
-          // (`released` of them so far), whether or not its tile reads it.
-          uint32_t waited = 0, released = 0;
-          auto wait_upto = [&](uint32_t idx) {
-            while (waited <= idx && ok) {
-              const uint32_t load = kv_base + waited;
-              ok = wait_bounded(wctx, bar_kv_full(slot_of(load)), parity_of(load), 0x200 + slot_of(load));
-              ++waited;
-            }
-          };
-          auto release_upto = [&](uint32_t idx) {      // hands back loads released..idx
-            while (released <= idx && ok) {
-              wait_upto(released);                     // one at a time: a later load may need this slot
-              if (ok) tc_commit(bar_kv_empty(slot_of(kv_base + released)));
-              ++released;
-            }
-          };
+          // The item's loads are K_0, V_0, K_1, V_1, ... = ld + 0, 1, 2, ...  Each is handed
+          // back to the producer exactly once by this thread, whether or not its tile reads
+          // it; `rel` is the next one to hand back.
+          const uint32_t ld_end = ld + 2u * static_cast<uint32_t>(w.nb);
+          uint32_t rel = ld;
           if (nsb > 0) {
             const uint32_t st = qn & 1u;
-            const uint64_t dq = desc_q(st);
+            const uint32_t q_lo = q_lo0 + st * (2u * kTile16);
+            const uint32_t b_qe = bar_q_empty(i, st);
             // Prologue: the first two S need no P.
-            wait_upto(0);
+            ok = kv_wait(ld);
             if (ok) ok = wait_bounded(wctx, bar_q_full(i, st), (qn >> 1) & 1u, 0x300 + i);
-            if (ok) {
-              tc_fence_after();
-              issue_qk(t_s, dq, desc_k(kv_base, 0));
-              tc_commit(bar_s_full(i, 0));
-              if (nsb > 1) {
-                issue_qk(t_s + kSubN, dq, desc_k(kv_base, 1));
-                tc_commit(bar_s_full(i, 1));
-              }
-              if (nsb <= 2) tc_commit(bar_q_empty(i, st));
-              release_upto(0);                                      // K_0
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(t_s0, q_lo, kv_lo(ld));
+            tc_commit(b_sf0);
+            if (nsb > 1) {
+              issue_qk(t_s1, q_lo, kv_lo(ld) + kKHalf);
+              tc_commit(b_sf1);
             }
-            // Step sb: PV(sb), then QK(sb+2) into the buffer PV just freed.
-            for (int sb = 0; sb < nsb && ok; ++sb) {
-              const int h = sb & 1;
-              const uint32_t j2 = static_cast<uint32_t>(sb) & ~1u;          // 2j
-              const bool has_qk = sb + 2 < nsb;
-              const uint32_t ts = t_s + h * kSubN;
-              const uint64_t dv = desc_v(kv_base + j2 + 1, h);
-              const uint64_t dk = desc_k(kv_base + j2 + 2, h);
-              wait_upto(has_qk ? j2 + 2 : j2 + 1);                           // V_j (and K_{j+1})
-              if (ok) ok = wait_bounded(wctx, bar_p_full(i, h), (h ? p_cnt1 : p_cnt0) & 1u, 0x400 + i);
-              if (sb == 0 && qn > 0 && ok)                                 // O_i of the previous item read out?
-                ok = wait_bounded(wctx, bar_o_free(i), (qn - 1) & 1u, 0x480 + i);
+            if (nsb <= 2) tc_commit(b_qe);
+            kv_release(ld);                                         // K_0
+            rel = ld + 1;
+            // Steps 2j and 2j+1: PV(sb), then QK(sb+2) into the S buffer PV just freed.
+            // Both read V_j; the QKs read the two halves of K_{j+1}.
+            const int n_pairs_kv = (nsb + 1) >> 1;
+            for (int j = 0; j < n_pairs_kv; ++j) {
+              const uint32_t lv = ld + 2u * j + 1u, lk = lv + 1u;   // loads V_j, K_{j+1}
+              const int sb = 2 * j;
+              const bool qk0 = sb + 2 < nsb, pv1 = sb + 1 < nsb, qk1 = sb + 3 < nsb;
+              const uint32_t v_lo = kv_lo(lv), k_lo = kv_lo(lk);
+              ok = kv_wait(lv);
+              if (qk0 && ok) ok = kv_wait(lk);
+              if (ok) ok = wait_bounded(wctx, b_pf0, pp0, 0x400 + i);
+              if (j == 0 && qn > 0 && ok)                            // O_i of the previous item read out?
+                ok = wait_bounded(wctx, b_ofree, (qn - 1) & 1u, 0x480 + i);
               if (!ok) break;
+              pp0 ^= 1u;
               tc_fence_after();
-              issue_pv(ts, dv, sb > 0);
-              tc_commit(bar_o_done(i));
-              if (sb == nsb - 1) tc_commit(bar_o_final(i));
-              if (has_qk) {
-                issue_qk(ts, dq, dk);
-                tc_commit(bar_s_full(i, h));                                 // S_i[h] now holds sub-block sb+2
-                if (sb + 2 == nsb - 1) tc_commit(bar_q_empty(i, st));
+              issue_pv(t_s0, v_lo, j > 0);
+              tc_commit(b_od);
+              if (!pv1) tc_commit(b_ofin);
+              if (qk0) {
+                issue_qk(t_s0, q_lo, k_lo);
+                tc_commit(b_sf0);                                    // S_i[0] now holds sub-block sb+2
+                if (sb + 2 == nsb - 1) tc_commit(b_qe);
               }
-              if (h) ++p_cnt1; else ++p_cnt0;
-              // V_j was last read by PV(2j+1), K_{j+1} by QK(2j+3), both issued in step 2j+1.
-              if (h == 1) release_upto(min(j2 + 2, n_loads - 1));
+              if (pv1) {
+                ok = wait_bounded(wctx, b_pf1, pp1, 0x400 + i);
+                if (!ok) break;
+                pp1 ^= 1u;
+                tc_fence_after();
+                issue_pv(t_s1, v_lo + 2u * kVStep, true);
+                tc_commit(b_od);
+                if (sb + 1 == nsb - 1) tc_commit(b_ofin);
+                if (qk1) {
+                  issue_qk(t_s1, q_lo, k_lo + kKHalf);
+                  tc_commit(b_sf1);                                  // S_i[1] now holds sub-block sb+3
+                  if (sb + 3 == nsb - 1) tc_commit(b_qe);
+                }
+              }
+              // V_j was last read by PV(2j+1), K_{j+1} by QK(2j+3).
+              kv_release(lv);
+              rel = lk;
+              if (qk0) {
+                kv_release(lk);
+                rel = lk + 1u;
+              }
             }
             ++qn;
           }
-          if (ok) release_upto(n_loads - 1);                          // whatever this tile did not read
-          kv_base += n_loads;
+          // Loads this tile did not read.  Waiting for each before handing it back keeps this
+          // thread from arriving twice in one phase of a slot's barrier: the load can only
+          // have been issued after both tiles handed back the slot's previous occupant.
+          for (; rel < ld_end && ok; ++rel) {
+            ok = kv_wait(rel);
+            if (ok) kv_release(rel);
+          }
+          ld = ld_end;
         }
       }
       if (!ok) {
