@@ -822,7 +822,9 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const float inv = ((l_tot == 0.f || l_tot != l_tot) ? 1.f : 1.f / l_tot) * o_scale;
         if (args.lse != nullptr && h == 0 && q_row < seqlen)    // log(sum exp(scale*s)) = scale*m + log(l)
           args.lse[static_cast<size_t>(w.bh) * seqlen + q_row] = m_fin * sm_scale + __logf(l_tot);
-        __half* o_row = args.o + (static_cast<size_t>(w.bh) * seqlen + q_row) * D + h * (D / 2);
+        // Rows of O are args.head_dim long; the kernel's columns beyond that are padding.
+        const int d_out = args.head_dim;
+        __half* o_row = args.o + (static_cast<size_t>(w.bh) * seqlen + q_row) * d_out + h * (D / 2);
 #pragma unroll
         for (int q = 0; q < D / 64; ++q) {
           uint32_t orow[32];
@@ -833,7 +835,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_o_free(i));      // the next item's PV may overwrite O_i
           }
-          if (q_row < seqlen) {
+          if (q_row < seqlen && h * (D / 2) + 32 * q < d_out) {       // head_dim is a multiple of 32
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
               st_global_v4(o_row + 32 * q + e,

@@ -16,6 +16,7 @@ struct KernelArgs {
   __half* o;                      // [batch*heads, seqlen, head_dim] fp16
   int seqlen;                     // query rows per slice
   int seqlen_k;                   // key/value rows per slice
+  int head_dim;                   // row length of Q, K, V and O (<= the kernel's head dim)
   int heads;                      // query heads per batch entry
   int heads_kv;                   // K/V heads per batch entry (divides heads)
   int n_pairs;                    // ceil(seqlen / 256): pairs of 128-row query tiles per slice

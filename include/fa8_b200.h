@@ -55,7 +55,7 @@ typedef struct fa8_fwd_params {
   int32_t batch;
   int32_t heads;
   int32_t seqlen;    /* query rows per head (and key rows unless seqlen_k says otherwise); multiple of 16 */
-  int32_t head_dim;  /* 64 or 128 */
+  int32_t head_dim;  /* 32, 64, 96 or 128 (32 and 96 run zero-padded to 64 and 128) */
   float softmax_scale; /* > 0; P = exp(softmax_scale * (S - rowmax)) */
   int32_t is_causal;   /* 0/1; mask is lower-triangular including the diagonal (test.py:25-33) */
   int32_t v_layout;    /* FA8_V_TRANSPOSED or FA8_V_NATURAL */

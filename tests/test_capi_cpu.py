@@ -36,7 +36,9 @@ def test_error_strings_and_support_query():
     assert lib.fa8_error_string(-99) == b"unknown fa8 status"
     assert lib.fa8_supported(4096, 128, _lib.FA8_V_TRANSPOSED) == _lib.FA8_OK
     assert lib.fa8_supported(128, 64, _lib.FA8_V_TRANSPOSED) == _lib.FA8_OK
-    assert lib.fa8_supported(128, 96, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
+    assert lib.fa8_supported(128, 96, _lib.FA8_V_TRANSPOSED) == _lib.FA8_OK
+    assert lib.fa8_supported(128, 32, _lib.FA8_V_NATURAL) == _lib.FA8_OK
+    assert lib.fa8_supported(128, 48, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
     assert lib.fa8_supported(100, 64, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
     assert lib.fa8_supported(0, 64, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
 
@@ -54,7 +56,7 @@ def test_argument_validation_needs_no_gpu():
     p.q = fake + 8
     assert lib.fa8_fwd(ctypes.byref(p), None) == _lib.FA8_ERR_BAD_ARG          # 16-byte alignment
     p.q = fake
-    p.head_dim = 96
+    p.head_dim = 48
     assert lib.fa8_fwd(ctypes.byref(p), None) == _lib.FA8_ERR_UNSUPPORTED
     p.head_dim = 64
     p.v_layout = 7

@@ -193,6 +193,25 @@ def test_different_query_and_key_lengths(Sq, Sk, causal):
     assert float((lse.cpu() - torch.logsumexp(s, dim=-1)).abs().max()) <= 2e-3
 
 
+@pytest.mark.parametrize("D", [32, 96])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("layout", ["transposed", "natural"])
+def test_head_dims_of_the_reference_switch_below_128(D, causal, layout):
+    """Head dims 32 and 96 (csrc/static_switch.h:50-77) run as zero-padded 64 / 128."""
+    d = dev()
+    B, H, S = 1, 3, 640
+    q8, k8, v8 = rand8(B, H, S, D, seed=D), rand8(B, H, S, D, seed=D + 1), rand8(B, H, S, D, seed=D + 2)
+    scale = 1 / math.sqrt(D)
+    v_arg = v8.to(d) if layout == "natural" else v8.to(d).transpose(2, 3).contiguous()
+    guard = torch.full((B * H * S * D + 64,), float("nan"), dtype=torch.float16, device=d)
+    out_buf = guard[:B * H * S * D].view(B, H, S, D)
+    out = flash_attention_v2_cutlass(q8.to(d), k8.to(d), v_arg, causal, scale, v_layout=layout, out=out_buf)[0]
+    check_status(d)
+    assert tuple(out.shape) == (B, H, S, D)
+    assert bool(torch.isnan(guard[B * H * S * D:]).all())        # nothing written past the last row
+    assert_close_to_oracles(out, q8, k8, v8, causal, scale)
+
+
 def test_known_answers():
     S, D = 512, 128
     q8, k8 = rand8(1, 2, S, D, seed=1), rand8(1, 2, S, D, seed=2)
@@ -239,9 +258,9 @@ def test_operator_argument_errors_on_gpu():
         flash_attention_v2_cutlass(q.float(), q, vt, False, 0.125)
     with pytest.raises(RuntimeError, match="v must be"):
         flash_attention_v2_cutlass(q, q, q, False, 0.125)               # V not transposed
-    q96 = torch.zeros(1, 1, 128, 96, device=d).to(F8)
+    q48 = torch.zeros(1, 1, 128, 48, device=d).to(F8)
     with pytest.raises(RuntimeError, match="unsupported"):
-        flash_attention_v2_cutlass(q96, q96, q96.transpose(2, 3).contiguous(), False, 0.125)
+        flash_attention_v2_cutlass(q48, q48, q48.transpose(2, 3).contiguous(), False, 0.125)
     with pytest.raises(RuntimeError, match="bad argument"):
         flash_attention_v2_cutlass(q, q, vt, False, 0.0)
     out = flash_attention_v2_cutlass(q, q, vt)                            # defaults: non-causal, scale 1
