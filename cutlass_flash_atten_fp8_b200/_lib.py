@@ -26,7 +26,7 @@ FA8_DTYPE_BF16 = 1
 # Every symbol include/fa8_b200.h declares.
 EXPORTED_SYMBOLS = ("fa8_fwd", "fa8_check_status", "fa8_supported", "fa8_error_string",
                     "fa8_last_error_detail", "fa8_version", "fa8_selftest_expired_wait",
-                    "fa8_quantize_e4m3")
+                    "fa8_quantize_e4m3", "fa8_quantize_e4m3_segments")
 
 
 class Fa8FwdParams(ctypes.Structure):
@@ -39,6 +39,7 @@ class Fa8FwdParams(ctypes.Structure):
         ("softmax_lse", ctypes.c_void_p), ("heads_kv", ctypes.c_int32),
         ("descale_q", ctypes.c_void_p), ("descale_k", ctypes.c_void_p), ("descale_v", ctypes.c_void_p),
         ("fp8_format", ctypes.c_int32), ("seqlen_k", ctypes.c_int32),
+        ("descale_per_head", ctypes.c_int32),
     ]
 
 
@@ -63,6 +64,9 @@ def load() -> ctypes.CDLL:
     lib.fa8_quantize_e4m3.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64,
                                       ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     lib.fa8_quantize_e4m3.restype = ctypes.c_int
+    lib.fa8_quantize_e4m3_segments.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64,
+                                               ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    lib.fa8_quantize_e4m3_segments.restype = ctypes.c_int
     lib.fa8_supported.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.fa8_supported.restype = ctypes.c_int
     lib.fa8_error_string.argtypes = [ctypes.c_int]

@@ -111,9 +111,15 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         _check_input(out, "out")
         if out.dtype != torch.float16 or tuple(out.shape) != (B, H, S, D) or out.device != q.device:
             raise RuntimeError("out must be a float16 CUDA tensor shaped like q")
-    for name, t in (("descale_q", descale_q), ("descale_k", descale_k), ("descale_v", descale_v)):
-        if t is not None and (t.dtype != torch.float32 or t.numel() != 1 or t.device != q.device):
-            raise RuntimeError(f"{name} must be a one-element float32 tensor on q's device")
+    # one float per tensor, or one per (batch, head): [B*H] for Q, [B*heads_kv] for K and V
+    given = [(n, t, full) for n, t, full in (("descale_q", descale_q, B * H), ("descale_k", descale_k, B * Hk),
+                                             ("descale_v", descale_v, B * Hk)) if t is not None]
+    per_head = any(t.numel() > 1 for _, t, _ in given)
+    for name, t, full in given:
+        if t.dtype != torch.float32 or t.device != q.device or not t.is_contiguous() or \
+                t.numel() != (full if per_head else 1):
+            raise RuntimeError(f"{name} must be a contiguous float32 tensor on q's device with one element, or "
+                               f"(all three alike) one per (batch, head): {full}")
     lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if return_lse else None
     p = _lib.Fa8FwdParams(
         q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=out.data_ptr(),
@@ -125,7 +131,7 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         descale_k=(descale_k.data_ptr() if descale_k is not None else None),
         descale_v=(descale_v.data_ptr() if descale_v is not None else None),
         fp8_format=(_lib.FA8_FP8_E5M2 if q.dtype == torch.float8_e5m2 else _lib.FA8_FP8_E4M3),
-        seqlen_k=Sk)
+        seqlen_k=Sk, descale_per_head=int(per_head))
     with torch.cuda.device(q.device):
         rc = lib.fa8_fwd(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
     if rc != _lib.FA8_OK:
@@ -133,24 +139,33 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     return [out, lse] if return_lse else [out]
 
 
-def quantize_e4m3(x: torch.Tensor):
-    """Per-tensor amax quantisation of a contiguous fp16 / bf16 CUDA tensor:
-    returns (x8, descale) with x8 = e4m3(x * 448 / max|x|) shaped like x and descale a
-    one-element fp32 tensor (x ~= descale * x8).  Stream-ordered, two HBM-bound kernels;
-    stands where the reference's callers cast with torch (test.py:20-22, 68-70)."""
+def quantize_e4m3(x: torch.Tensor, per_head: bool = False):
+    """Amax quantisation of a contiguous fp16 / bf16 CUDA tensor: returns (x8, descale) with
+    x8 = e4m3(x * 448 / max|x|) shaped like x and x ~= descale * x8.  Per tensor, descale is a
+    one-element fp32 tensor; with per_head=True x is [batch, heads, ...] and every (batch,
+    head) slice gets its own scale: descale is [batch*heads].  Stream-ordered, two HBM-bound
+    kernels; stands where the reference's callers cast with torch (test.py:20-22, 68-70)."""
     lib = _lib.load()
     _check_input(x, "x")
     if x.dtype not in (torch.float16, torch.bfloat16):
         raise RuntimeError(f"x must be float16 or bfloat16, got {x.dtype}")
+    dt = _lib.FA8_DTYPE_BF16 if x.dtype == torch.bfloat16 else _lib.FA8_DTYPE_FP16
     x8 = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
-    scal = torch.empty(2, dtype=torch.float32, device=x.device)       # [amax, descale]
+    n_seg = x.shape[0] * x.shape[1] if per_head else 1
+    scal = torch.empty(2 * n_seg, dtype=torch.float32, device=x.device)       # [amax..., descale...]
     with torch.cuda.device(x.device):
-        rc = lib.fa8_quantize_e4m3(x.data_ptr(), _lib.FA8_DTYPE_BF16 if x.dtype == torch.bfloat16 else _lib.FA8_DTYPE_FP16,
-                                   x8.data_ptr(), x.numel(), scal.data_ptr(), scal.data_ptr() + 4,
-                                   torch.cuda.current_stream(x.device).cuda_stream)
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        if per_head:
+            if x.dim() < 3:
+                raise RuntimeError("per_head needs a [batch, heads, ...] tensor")
+            rc = lib.fa8_quantize_e4m3_segments(x.data_ptr(), dt, x8.data_ptr(), x.numel() // n_seg, n_seg,
+                                                scal.data_ptr(), scal.data_ptr() + 4 * n_seg, stream)
+        else:
+            rc = lib.fa8_quantize_e4m3(x.data_ptr(), dt, x8.data_ptr(), x.numel(), scal.data_ptr(),
+                                       scal.data_ptr() + 4, stream)
     if rc != _lib.FA8_OK:
         raise RuntimeError(_lib.error_message(rc))
-    return x8, scal[1:2]
+    return x8, scal[n_seg:]
 
 
 class HostRunner:

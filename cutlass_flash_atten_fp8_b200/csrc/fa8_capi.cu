@@ -74,7 +74,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 extern "C" {
 
-int fa8_version(void) { return 105; }
+int fa8_version(void) { return 106; }
 
 const char* fa8_error_string(int code) {
   switch (code) {
@@ -149,6 +149,7 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   args.descale_q = p->descale_q;
   args.descale_k = p->descale_k;
   args.descale_v = p->descale_v;
+  args.descale_per_head = p->descale_per_head != 0;
   args.heads = p->heads;
   args.heads_kv = heads_kv;
   args.softmax_scale = p->softmax_scale;
@@ -174,7 +175,23 @@ int fa8_quantize_e4m3(const void* src, int32_t src_dtype, void* dst, int64_t n, 
   if (src_dtype != FA8_DTYPE_FP16 && src_dtype != FA8_DTYPE_BF16) return FA8_ERR_BAD_ARG;
   if (!aligned16(src) || !aligned16(dst)) return FA8_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(amax) & 3u) || (reinterpret_cast<uintptr_t>(descale) & 3u)) return FA8_ERR_BAD_ARG;
-  cudaError_t e = fa8::launch_quantize(src, src_dtype == FA8_DTYPE_BF16, dst, n, amax, descale,
+  cudaError_t e = fa8::launch_quantize(src, src_dtype == FA8_DTYPE_BF16, dst, n, 1, amax, descale,
+                                       static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) {
+    set_detail("quantize launch", cudaGetErrorString(e));
+    return FA8_ERR_CUDA;
+  }
+  return FA8_OK;
+}
+
+int fa8_quantize_e4m3_segments(const void* src, int32_t src_dtype, void* dst, int64_t seg_len, int32_t n_seg,
+                               float* amax, float* descale, void* cuda_stream) {
+  g_detail[0] = '\0';
+  if (!src || !dst || !amax || seg_len <= 0 || n_seg <= 0 || n_seg > 65535) return FA8_ERR_BAD_ARG;
+  if (src_dtype != FA8_DTYPE_FP16 && src_dtype != FA8_DTYPE_BF16) return FA8_ERR_BAD_ARG;
+  if (!aligned16(src) || !aligned16(dst) || (seg_len % 8) != 0) return FA8_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(amax) & 3u) || (reinterpret_cast<uintptr_t>(descale) & 3u)) return FA8_ERR_BAD_ARG;
+  cudaError_t e = fa8::launch_quantize(src, src_dtype == FA8_DTYPE_BF16, dst, seg_len, n_seg, amax, descale,
                                        static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess) {
     set_detail("quantize launch", cudaGetErrorString(e));

@@ -677,12 +677,16 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t t_o = tmem_base + lane_sel + kTmemO + i * D;
     // Per-tensor descales that live on the device (written by the quantisation pre-pass)
     // fold into the softmax scale (Q, K) and the output scale (V).
+    // With descale_per_head they are arrays, one entry per (batch, head) for Q and per
+    // (batch, key/value head) for K and V, re-read for every work item.
     float qk_descale = 1.f, o_scale = args.o_scale;
-    if (args.descale_q != nullptr) qk_descale *= __ldg(args.descale_q);
-    if (args.descale_k != nullptr) qk_descale *= __ldg(args.descale_k);
-    if (args.descale_v != nullptr) o_scale *= __ldg(args.descale_v);
-    const float c = args.scale_log2 * qk_descale;
-    const float sm_scale = args.softmax_scale * qk_descale;
+    if (!args.descale_per_head) {
+      if (args.descale_q != nullptr) qk_descale *= __ldg(args.descale_q);
+      if (args.descale_k != nullptr) qk_descale *= __ldg(args.descale_k);
+      if (args.descale_v != nullptr) o_scale *= __ldg(args.descale_v);
+    }
+    float c = args.scale_log2 * qk_descale;
+    float sm_scale = args.softmax_scale * qk_descale;
     RowGroupShared& grp = groups[i * 4 + quarter];
     // Running phase counts of the barriers this warp waits on.
     uint32_t own_cnt = 0;        // sub-blocks taken from my S buffer: s_full[i][h] phases consumed
@@ -704,6 +708,18 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int q_row = w.row0 + i * kTileM + row;       // global query row, may be >= seqlen
         const int col_lim = kCausal ? min(args.seqlen_k, q_row + 1) : args.seqlen_k;   // keys this row may see
         const uint32_t ib = items & 1u;
+        if (args.descale_per_head) {
+          const int b_idx = w.bh / args.heads;
+          const int kv_bh = b_idx * args.heads_kv + (w.bh - b_idx * args.heads) / (args.heads / args.heads_kv);
+          qk_descale = 1.f;
+          o_scale = args.o_scale;
+          if (args.descale_q != nullptr) qk_descale *= __ldg(args.descale_q + w.bh);
+          if (args.descale_k != nullptr) qk_descale *= __ldg(args.descale_k + kv_bh);
+          if (args.descale_v != nullptr) o_scale *= __ldg(args.descale_v + kv_bh);
+          c = args.scale_log2 * qk_descale;
+          sm_scale = args.softmax_scale * qk_descale;
+          ek.set_scale(c);
+        }
         // m is the row maximum the exponentials are taken against, shared by the two warps
         // of the row group through grp.m / grp.version: exact after sub-block 0, then raised
         // only by the exact path below.  l is this warp's share of the row sum, kept relative

@@ -26,6 +26,7 @@ struct KernelArgs {
   const float* descale_q;         // optional device scalars: softmax scale *= dq*dk, O *= dv
   const float* descale_k;
   const float* descale_v;
+  int descale_per_head;           // the three are arrays: [batch*heads] for Q, [batch*heads_kv] for K, V
   float* lse;                     // optional [batch*heads, seqlen] fp32: log-sum-exp of the scaled scores
   float softmax_scale;            // as given by the caller (natural-log units, for lse)
   int* status;                    // optional device word; non-zero after a bounded wait expired
@@ -43,9 +44,10 @@ cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, con
 // One warp waits (bounded by limit_ns) on a barrier that never completes; see fa8_selftest_expired_wait.
 cudaError_t launch_expired_wait(int* status, unsigned long long limit_ns, cudaStream_t stream);
 
-// Per-tensor amax quantisation fp16/bf16 -> e4m3 (fa8_quant.cu): *amax = max|src|,
-// dst = e4m3(src * 448 / amax), *descale = amax / 448 (descale may be null).
-cudaError_t launch_quantize(const void* src, bool bf16, void* dst, int64_t n, float* amax, float* descale,
-                            cudaStream_t stream);
+// Amax quantisation fp16/bf16 -> e4m3 (fa8_quant.cu) of n_seg contiguous segments of n
+// elements each: amax[s] = max|src_s|, dst_s = e4m3(src_s * 448 / amax[s]),
+// descale[s] = amax[s] / 448 (descale may be null).
+cudaError_t launch_quantize(const void* src, bool bf16, void* dst, int64_t n, int n_seg, float* amax,
+                            float* descale, cudaStream_t stream);
 
 }  // namespace fa8

@@ -8,7 +8,9 @@
 //           descale = amax / 448       saturating (cvt.rn.satfinite.e4m3x2.f32)
 //
 // Both use 16-byte loads, a grid of a few CTAs per SM and grid-stride loops.  amax and descale
-// are caller-provided device floats (outputs); nothing else is written.
+// are caller-provided device floats (outputs); nothing else is written.  With n_seg > 1 the
+// tensor is n_seg equal, contiguous segments (one per head, say), each with its own amax and
+// descale: blockIdx.y picks the segment.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -38,6 +40,8 @@ template <bool kBf16>
 __global__ void __launch_bounds__(kQuantThreads) amax_kernel(const uint4* __restrict__ x, int64_t n_vec,
                                                             const uint16_t* __restrict__ tail, int n_tail,
                                                             float* __restrict__ amax) {
+  x += blockIdx.y * n_vec;
+  amax += blockIdx.y;
   float m = 0.f;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n_vec;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -73,6 +77,10 @@ __global__ void __launch_bounds__(kQuantThreads) cast_kernel(const uint4* __rest
                                                             uint8_t* __restrict__ tail_out, int n_tail,
                                                             const float* __restrict__ amax,
                                                             float* __restrict__ descale) {
+  x += blockIdx.y * n_vec;
+  y += blockIdx.y * n_vec;
+  amax += blockIdx.y;
+  if (descale != nullptr) descale += blockIdx.y;
   const float a = *amax;
   const float scale = a > 0.f ? 448.f / a : 1.f;
   if (blockIdx.x == 0 && threadIdx.x == 0 && descale != nullptr) *descale = a > 0.f ? a / 448.f : 1.f;
@@ -94,21 +102,24 @@ __global__ void __launch_bounds__(kQuantThreads) cast_kernel(const uint4* __rest
 
 }  // namespace
 
-cudaError_t launch_quantize(const void* src, bool bf16, void* dst, int64_t n, float* amax, float* descale,
-                            cudaStream_t stream) {
+cudaError_t launch_quantize(const void* src, bool bf16, void* dst, int64_t n, int n_seg, float* amax,
+                            float* descale, cudaStream_t stream) {
   int dev = 0, sms = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) return e;
+  // n = elements per segment; segments other than a lone one are whole 16-byte vectors
   const int64_t n_vec = n / 8;
   const int n_tail = static_cast<int>(n - n_vec * 8);
-  int64_t want = (n_vec + kQuantThreads - 1) / kQuantThreads;
-  const int grid = static_cast<int>(want < 1 ? 1 : (want > 8ll * sms ? 8ll * sms : want));
+  if (n_seg < 1 || n_seg > 65535 || (n_seg > 1 && n_tail != 0)) return cudaErrorInvalidValue;
+  const int64_t want = (n_vec + kQuantThreads - 1) / kQuantThreads;
+  const int64_t cap = (8ll * sms + n_seg - 1) / n_seg;      // about eight CTAs per SM in all
+  const dim3 grid(static_cast<unsigned>(want < 1 ? 1 : (want > cap ? cap : want)), static_cast<unsigned>(n_seg), 1);
   const uint4* x = static_cast<const uint4*>(src);
   const uint16_t* tail_in = static_cast<const uint16_t*>(src) + n_vec * 8;
   uint8_t* tail_out = static_cast<uint8_t*>(dst) + n_vec * 8;
-  e = cudaMemsetAsync(amax, 0, sizeof(float), stream);
+  e = cudaMemsetAsync(amax, 0, sizeof(float) * n_seg, stream);
   if (e != cudaSuccess) return e;
   if (bf16) {
     amax_kernel<true><<<grid, kQuantThreads, 0, stream>>>(x, n_vec, tail_in, n_tail, amax);

@@ -86,6 +86,9 @@ typedef struct fa8_fwd_params {
                            causal mask stays aligned top-left (key index <= query index), as in the
                            reference (csrc/flash_attention.cu:24-71); the reference carries q_seqlen and
                            k_seqlen separately (csrc/flash.h) but its test only runs them equal. */
+  int32_t descale_per_head; /* 0: descale_q/k/v point to one float each (per tensor).  1: to arrays, one
+                               float per (batch, head) for Q ([batch*heads]) and per (batch, K/V head)
+                               for K and V ([batch*heads_kv]), as fa8_quantize_e4m3_segments writes them. */
 } fa8_fwd_params;
 
 /* Enqueues the forward on `cuda_stream` (a cudaStream_t; NULL = default stream)
@@ -111,6 +114,13 @@ int fa8_check_status(const int32_t* status_word, void* cuda_stream, int32_t* cod
 int fa8_quantize_e4m3(const void* src, int32_t src_dtype, void* dst, int64_t n, float* amax,
                       float* descale, void* cuda_stream);
 
+/* The same for `n_seg` equal contiguous segments of `seg_len` values (a multiple of 8), each
+ * with its own scale: amax[s], descale[s] for s < n_seg (<= 65535).  With seg_len = seqlen *
+ * head_dim and n_seg = batch * heads this is per-head quantisation of a [batch, heads, seqlen,
+ * head_dim] tensor, matching descale_per_head of fa8_fwd_params. */
+int fa8_quantize_e4m3_segments(const void* src, int32_t src_dtype, void* dst, int64_t seg_len,
+                               int32_t n_seg, float* amax, float* descale, void* cuda_stream);
+
 /* Failure-detection self-test (no counterpart in the reference, whose only error path is
  * exit(), include/attention_api.cuh:20-29): enqueues a one-warp kernel that waits on a barrier
  * nobody completes, using the same bounded wait as the attention kernel.  After `limit_us`
@@ -131,7 +141,8 @@ const char* fa8_error_string(int code);
 const char* fa8_last_error_detail(void);
 
 /* ABI version of this header: major*100 + minor (101 added softmax_lse, 102 heads_kv, 103 the
- * descale pointers and fa8_quantize_e4m3, 104 fp8_format, 105 seqlen_k; new fields go at
+ * descale pointers and fa8_quantize_e4m3, 104 fp8_format, 105 seqlen_k, 106 descale_per_head and
+ * fa8_quantize_e4m3_segments; new fields go at
  * the end of fa8_fwd_params). */
 int fa8_version(void);
 
