@@ -90,7 +90,7 @@ const char* fa8_error_string(int code) {
 const char* fa8_last_error_detail(void) { return g_detail; }
 
 int fa8_supported(int32_t seqlen, int32_t head_dim, int32_t v_layout) {
-  if (head_dim != 32 && head_dim != 64 && head_dim != 96 && head_dim != 128) return FA8_ERR_UNSUPPORTED;
+  if (head_dim < 32 || head_dim > 256 || (head_dim % 32) != 0) return FA8_ERR_UNSUPPORTED;
   if (seqlen <= 0 || (seqlen % 16) != 0) return FA8_ERR_UNSUPPORTED;
   if (v_layout != FA8_V_TRANSPOSED && v_layout != FA8_V_NATURAL) return FA8_ERR_UNSUPPORTED;
   return FA8_OK;
@@ -121,17 +121,20 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   if (fa8_supported(seqlen_k, p->head_dim, p->v_layout) != FA8_OK) return FA8_ERR_UNSUPPORTED;
   const uint64_t S = static_cast<uint64_t>(p->seqlen), D = static_cast<uint64_t>(p->head_dim);
   const uint64_t Sk = static_cast<uint64_t>(seqlen_k);
-  // The kernel is built for head dims 64 and 128.  32 and 96 run on the next one up: the
-  // tensor maps keep the true extent and the copy engine fills the box's missing columns
-  // (rows, for V^T) with zeros, which add nothing to either product.
-  const uint32_t d_box = (p->head_dim <= 64) ? 64u : 128u;
-  const CUtensorMapSwizzle sw_qk = (d_box == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  // The kernel is built for head dims 64, 128 and 256 (the reference's switch has eight
+  // buckets, csrc/static_switch.h:50-77).  The others run on the next one up: the tensor maps
+  // keep the true extent and the copy engine fills the box's missing columns (rows, for V^T)
+  // with zeros, which add nothing to either product.  Rows longer than 128 bytes are copied as
+  // column blocks of 128 bytes.
+  const uint32_t d_box = (p->head_dim <= 64) ? 64u : (p->head_dim <= 128 ? 128u : 256u);
+  const uint32_t d_blk = d_box < 128u ? d_box : 128u;
+  const CUtensorMapSwizzle sw_qk = (d_box >= 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap tq, tk, tv;
-  if (!make_map_3d(&tq, p->q, D, S, bh, d_box, 128, sw_qk)) return FA8_ERR_CUDA;
-  if (!make_map_3d(&tk, p->k, D, Sk, bh_kv, d_box, 128, sw_qk)) return FA8_ERR_CUDA;
+  if (!make_map_3d(&tq, p->q, D, S, bh, d_blk, 128, sw_qk)) return FA8_ERR_CUDA;
+  if (!make_map_3d(&tk, p->k, D, Sk, bh_kv, d_blk, 128, sw_qk)) return FA8_ERR_CUDA;
   if (p->v_layout == FA8_V_NATURAL) {
     // V: [bh, S, D] like K; a tile is 128 key rows of D bytes.
-    if (!make_map_3d(&tv, p->v, D, Sk, bh_kv, d_box, 128, sw_qk)) return FA8_ERR_CUDA;
+    if (!make_map_3d(&tv, p->v, D, Sk, bh_kv, d_blk, 128, sw_qk)) return FA8_ERR_CUDA;
   } else {
     // V^T: [bh, D, S]; a tile is D rows of 128 consecutive key positions.
     if (!make_map_3d(&tv, p->v, Sk, D, bh_kv, 128, d_box, CU_TENSOR_MAP_SWIZZLE_128B)) return FA8_ERR_CUDA;
@@ -154,7 +157,9 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   args.heads_kv = heads_kv;
   args.softmax_scale = p->softmax_scale;
   args.timeout_ns = 2000000000ull;
-  args.n_pairs = (p->seqlen + 255) / 256;
+  // work items hold two 128-row query tiles, one at head_dim 256 (see the kernel's Cfg)
+  const int rows_per_item = (d_box == 256u) ? 128 : 256;
+  args.n_pairs = (p->seqlen + rows_per_item - 1) / rows_per_item;
   const int64_t per_slice = p->is_causal ? (args.n_pairs + 1) / 2 : args.n_pairs;
   if (bh * per_slice > 0x7fffffff) return FA8_ERR_UNSUPPORTED;
   args.n_units = static_cast<int>(bh * per_slice);

@@ -70,10 +70,17 @@ constexpr uint32_t kTmemO = 256;   // first O column; S_0 at 0, S_1 at 128
 
 template <int D>
 struct Cfg {
-  static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
+  static_assert(D == 64 || D == 128 || D == 256, "head_dim must be 64, 128 or 256");
+  // Rows longer than 128 bytes are stored as column blocks of 128 bytes, one after the other
+  // (each block a 128-row swizzled tile of its own).
+  static constexpr int kBlkD = (D < 128) ? D : 128;    // bytes per row of a column block
+  static constexpr int kNBlk = D / kBlkD;
+  static constexpr int kBlkBytes = 128 * kBlkD;
   static constexpr int kTileBytes = 128 * D;           // Q, K and V^T tiles alike
-  static constexpr int kSlots = (D == 128) ? 8 : 16;   // ring slots, one K or V tile each
-  static constexpr int kQBytes = 4 * kTileBytes;           // two tiles x two stages (work items)
+  // Query tiles per CTA: two, or one where O alone takes half of tensor memory (head_dim 256).
+  static constexpr int kTiles = (D <= 128) ? 2 : 1;
+  static constexpr int kSlots = (D == 128) ? 8 : (D == 64 ? 16 : 4);   // ring slots, one K or V tile each
+  static constexpr int kQBytes = 2 * kTiles * kTileBytes;  // tiles x two stages (work items)
   static constexpr int kRingBytes = kSlots * kTileBytes;
   static constexpr int kBarOffset = kQBytes + kRingBytes;
   // row-group scratch shared by the two warps of a 32-row group, see RowGroupShared
@@ -82,8 +89,8 @@ struct Cfg {
                                   2 /*o_done*/ + 2 /*o_final*/ + 2 /*o_free*/ + 2 /*drain*/;
   static constexpr int kSmemBytes = kBarOffset + kNumBars * 8 + 16 /*tmem ptr, abort*/ + kGroupBytes + 1024 /*align*/;
   // Q and K rows are D bytes long: one 128-byte swizzle row for D=128, a 64-byte one for D=64.
-  static constexpr uint32_t kQKLayout = (D == 128) ? 2u : 4u;   // UMMA SWIZZLE_128B / SWIZZLE_64B
-  static constexpr uint32_t kQKSbo = 8 * D;                      // bytes between 8-row groups
+  static constexpr uint32_t kQKLayout = (D >= 128) ? 2u : 4u;   // UMMA SWIZZLE_128B / SWIZZLE_64B
+  static constexpr uint32_t kQKSbo = 8 * kBlkD;                  // bytes between 8-row groups
 };
 
 // Shared-memory matrix descriptor for a K-major swizzled operand tile (rows of at most 128
@@ -301,7 +308,7 @@ struct RowGroupShared {
 };
 static_assert(sizeof(RowGroupShared) == 1184, "RowGroupShared layout");
 
-// One work item: two 128-row query tiles of one (batch, head) slice.
+// One work item: two 128-row query tiles of one (batch, head) slice (one tile at head_dim 256).
 struct Item {
   int bh;          // slice
   int row0;        // first query row of tile 0
@@ -315,7 +322,7 @@ struct Item {
 // the same few slices, whose K and V stay in L2).  Causal: the cost of a pair grows with
 // its position, so a unit folds pair f with pair n-1-f of the same slice (heavy one
 // first) and every unit costs the same.
-template <bool kCausal>
+template <bool kCausal, int kTiles>
 __device__ __forceinline__ bool get_item(const KernelArgs& a, int unit, int k, Item& it) {
   const int n_pairs = a.n_pairs;
   int pair;
@@ -335,12 +342,12 @@ __device__ __forceinline__ bool get_item(const KernelArgs& a, int unit, int k, I
       pair = f;
     }
   }
-  it.row0 = pair * 2 * kTileM;
+  it.row0 = pair * kTiles * kTileM;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int r0 = it.row0 + i * kTileM;
     int n = 0;
-    if (r0 < a.seqlen) {
+    if (i < kTiles && r0 < a.seqlen) {
       // one past the last visible key; the causal mask is aligned top-left (key <= query row),
       // like the reference's (csrc/flash_attention.cu:24-71, test.py:25-33)
       const int col_end = kCausal ? min(r0 + kTileM, a.seqlen_k) : a.seqlen_k;
@@ -450,20 +457,26 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       bool ok = true;
       int it = 0;                 // K/V loads issued so far; slot = it % kSlots
       int qn[2] = {0, 0};         // Q loads issued so far per tile; stage = qn & 1
-      auto load_kv = [&](const CUtensorMap* tm, int c0, int c1, int bh) {
+      // One tile of 128 rows of head_dim bytes (Q, K, natural V): a copy per 128-byte column block.
+      auto load_rows = [&](uint32_t dst, const CUtensorMap* tm, uint32_t bar, int row, int bh) {
+#pragma unroll
+        for (int b = 0; b < C::kNBlk; ++b) tma_load_3d(dst + b * C::kBlkBytes, tm, bar, b * C::kBlkD, row, bh);
+      };
+      auto load_kv = [&](const CUtensorMap* tm, bool rows, int c0, int c1, int bh) {
         const int slot = it % C::kSlots;
         const uint32_t round = static_cast<uint32_t>(it / C::kSlots);
         if (ok) ok = wait_bounded(wctx, bar_kv_empty(slot), (round & 1u) ^ 1u, 0x100 + slot);
         if (ok) {
           mbar_arrive_expect_tx(bar_kv_full(slot), C::kTileBytes);
-          tma_load_3d(s_ring + slot * C::kTileBytes, tm, bar_kv_full(slot), c0, c1, bh);
+          if (rows) load_rows(s_ring + slot * C::kTileBytes, tm, bar_kv_full(slot), c1, bh);
+          else tma_load_3d(s_ring + slot * C::kTileBytes, tm, bar_kv_full(slot), c0, c1, bh);
           ++it;
         }
       };
       for (int unit = blockIdx.x; unit < args.n_units && ok; unit += gridDim.x) {
         for (int k = 0; k < kItemsPerUnit && ok; ++k) {
           Item w;
-          if (!get_item<kCausal>(args, unit, k, w)) continue;
+          if (!get_item<kCausal, C::kTiles>(args, unit, k, w)) continue;
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
             if (w.nsb_t[i] > 0 && ok) {
@@ -472,8 +485,8 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               ok = wait_bounded(wctx, bar_q_empty(i, st), (round & 1u) ^ 1u, 0x180 + i);
               if (ok) {
                 mbar_arrive_expect_tx(bar_q_full(i, st), C::kTileBytes);
-                tma_load_3d(s_q + (2 * st + i) * C::kTileBytes, &tm_q, bar_q_full(i, st), 0,
-                            w.row0 + i * kTileM, w.bh);
+                load_rows(s_q + (C::kTiles * st + i) * C::kTileBytes, &tm_q, bar_q_full(i, st),
+                          w.row0 + i * kTileM, w.bh);
                 ++qn[i];
               }
             }
@@ -482,9 +495,9 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           const int b_idx = w.bh / args.heads;
           const int kv_bh = b_idx * args.heads_kv + (w.bh - b_idx * args.heads) / (args.heads / args.heads_kv);
           for (int j = 0; j < w.nb && ok; ++j) {
-            load_kv(&tm_k, 0, j * kBlockN, kv_bh);
-            if (kVNatural) load_kv(&tm_v, 0, j * kBlockN, kv_bh);    // [keys, head_dim] rows
-            else load_kv(&tm_v, j * kBlockN, 0, kv_bh);              // [head_dim, keys] rows
+            load_kv(&tm_k, true, 0, j * kBlockN, kv_bh);
+            if (kVNatural) load_kv(&tm_v, true, 0, j * kBlockN, kv_bh);    // [keys, head_dim] rows
+            else load_kv(&tm_v, false, j * kBlockN, 0, kv_bh);             // [head_dim, keys] rows
           }
         }
       }
@@ -522,10 +535,12 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       constexpr uint32_t kFmt = kE5M2 ? 1u : 0u;
       constexpr uint32_t kIdescQK = umma_idesc(kTileM, kSubN, kFmt);
       // V in its natural [keys, head_dim] layout is an MN-major B operand (bit 16).
-      constexpr uint32_t kIdescPV = umma_idesc(kTileM, D, kFmt) | (kVNatural ? (1u << 16) : 0u);
+      constexpr uint32_t kIdescPV = umma_idesc(kTileM, C::kBlkD, kFmt) | (kVNatural ? (1u << 16) : 0u);
+      constexpr uint32_t kBlk16 = C::kBlkBytes / 16;       // one column block in descriptor address units
       constexpr uint32_t kSlotMask = C::kSlots - 1;
       static_assert((C::kSlots & (C::kSlots - 1)) == 0, "ring size must be a power of two");
-      constexpr int kSlotShift = (C::kSlots == 8) ? 3 : 4;
+      constexpr int kSlotShift = (C::kSlots == 4) ? 2 : (C::kSlots == 8 ? 3 : 4);
+      static_assert((1 << kSlotShift) == C::kSlots, "ring size");
       constexpr uint32_t kTile16 = C::kTileBytes / 16;     // one tile in descriptor address units
       // This one thread paces the whole tile, so its instruction count per step is kept low:
       // descriptors are 32-bit low words (start address in units of 16 bytes; the high word
@@ -543,19 +558,25 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // sub-block h covers bytes 64h..64h+63 of every row = K-steps 2h and 2h+1.  In the
       // natural layout the tile is 128 key rows of D bytes (swizzled like K): a K-step of 32
       // keys is 32 rows further down.
-      constexpr uint32_t kVStep = kVNatural ? (32u * D / 16u) : 2u;   // descriptor units per 32 keys
-      constexpr uint32_t kKHalf = kSubN * D / 16;                     // rows 64..127 of a K tile
+      constexpr uint32_t kVStep = kVNatural ? (32u * C::kBlkD / 16u) : 2u;   // descriptor units per 32 keys
+      constexpr uint32_t kKHalf = kSubN * C::kBlkD / 16;                     // rows 64..127 of a K tile
       // S_i[h] = Q_i K_sb^T: D/32 steps of K = 32 bytes along the swizzled rows.
       auto issue_qk = [&](uint32_t ts, uint32_t q_lo, uint32_t k_lo) {
 #pragma unroll
-        for (int k = 0; k < D / 32; ++k)
-          mma_f8_ss(ts, make_desc(q_lo + 2u * k, qk_hi), make_desc(k_lo + 2u * k, qk_hi), kIdescQK, k > 0);
+        for (int k = 0; k < D / 32; ++k) {
+          // K-step k lies in column block k / 4 (four steps of 32 bytes per 128-byte row)
+          const uint32_t off = (C::kNBlk > 1 ? (k >> 2) * kBlk16 : 0u) + 2u * (C::kNBlk > 1 ? (k & 3) : k);
+          mma_f8_ss(ts, make_desc(q_lo + off, qk_hi), make_desc(k_lo + off, qk_hi), kIdescQK, k > 0);
+        }
       };
       // O_i (+)= P_i(sb) V_sb: P is 128 rows x 64 fp8 = 16 TMEM columns over S_i[h].
       auto issue_pv = [&](uint32_t ts, uint32_t v_lo, bool acc) {
 #pragma unroll
-        for (int k = 0; k < kSubN / 32; ++k)
-          mma_f8_ts(t_o, ts + 8u * k, make_desc(v_lo + kVStep * k, v_hi), kIdescPV, (acc || k > 0) ? 1u : 0u);
+        for (int nb = 0; nb < C::kNBlk; ++nb)         // 128 output columns per MMA: one column block of V
+#pragma unroll
+          for (int k = 0; k < kSubN / 32; ++k)
+            mma_f8_ts(t_o + nb * C::kBlkD, ts + 8u * k, make_desc(v_lo + nb * kBlk16 + kVStep * k, v_hi), kIdescPV,
+                      (acc || k > 0) ? 1u : 0u);
       };
       auto kv_wait = [&](uint32_t load) {
         const uint32_t slot = load & kSlotMask;
@@ -572,7 +593,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       for (int unit = blockIdx.x; unit < args.n_units && ok; unit += gridDim.x) {
         for (int kk = 0; kk < kItemsPerUnit && ok; ++kk) {
           Item w;
-          if (!get_item<kCausal>(args, unit, kk, w)) continue;
+          if (!get_item<kCausal, C::kTiles>(args, unit, kk, w)) continue;
           const int nsb = (i == 0) ? w.nsb_t[0] : w.nsb_t[1];
           // The item's loads are K_0, V_0, K_1, V_1, ... = ld + 0, 1, 2, ...  Each is handed
           // back to the producer exactly once by this thread, whether or not its tile reads
@@ -581,7 +602,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           uint32_t rel = ld;
           if (nsb > 0) {
             const uint32_t st = qn & 1u;
-            const uint32_t q_lo = q_lo0 + st * (2u * kTile16);
+            const uint32_t q_lo = q_lo0 + st * (C::kTiles * kTile16);
             const uint32_t b_qe = bar_q_empty(i, st);
             // Prologue: the first two S need no P.
             ok = kv_wait(ld);
@@ -702,7 +723,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int unit = blockIdx.x; unit < args.n_units && ok; unit += gridDim.x) {
       for (int kk = 0; kk < kItemsPerUnit && ok; ++kk) {
         Item w;
-        if (!get_item<kCausal>(args, unit, kk, w)) continue;
+        if (!get_item<kCausal, C::kTiles>(args, unit, kk, w)) continue;
         const int tile_nsb = w.nsb_t[i];
         if (tile_nsb == 0) continue;
         const int q_row = w.row0 + i * kTileM + row;       // global query row, may be >= seqlen
@@ -959,6 +980,10 @@ cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, con
   if (head_dim == 64) {
     return causal ? launch_layout<64, true>(v_natural, e5m2, tq, tk, tv, args, stream)
                   : launch_layout<64, false>(v_natural, e5m2, tq, tk, tv, args, stream);
+  }
+  if (head_dim == 256) {
+    return causal ? launch_layout<256, true>(v_natural, e5m2, tq, tk, tv, args, stream)
+                  : launch_layout<256, false>(v_natural, e5m2, tq, tk, tv, args, stream);
   }
   return cudaErrorInvalidValue;
 }

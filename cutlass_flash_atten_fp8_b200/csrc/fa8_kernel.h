@@ -19,7 +19,8 @@ struct KernelArgs {
   int head_dim;                   // row length of Q, K, V and O (<= the kernel's head dim)
   int heads;                      // query heads per batch entry
   int heads_kv;                   // K/V heads per batch entry (divides heads)
-  int n_pairs;                    // ceil(seqlen / 256): pairs of 128-row query tiles per slice
+  int n_pairs;                    // work items per slice: ceil(seqlen / 256), two 128-row query tiles each
+                                  // (ceil(seqlen / 128), one tile each, at head_dim 256)
   int n_units;                    // work units of the persistent grid (see get_item)
   float scale_log2;               // softmax_scale * log2(e)
   float o_scale;                  // multiplies O/l (1 = reference behaviour)
@@ -33,7 +34,7 @@ struct KernelArgs {
   unsigned long long timeout_ns;  // bound of every mbarrier wait
 };
 
-// Launches the persistent forward kernel for head_dim in {64,128}.
+// Launches the persistent forward kernel for head_dim in {64,128,256}.
 // v_natural: V is [slices, seqlen, head_dim] (tv describes it like K) instead of the
 // reference's transposed [slices, head_dim, seqlen].
 // e5m2: Q, K, V (and P) are e5m2 instead of e4m3.

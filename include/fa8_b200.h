@@ -55,7 +55,9 @@ typedef struct fa8_fwd_params {
   int32_t batch;
   int32_t heads;
   int32_t seqlen;    /* query rows per head (and key rows unless seqlen_k says otherwise); multiple of 16 */
-  int32_t head_dim;  /* 32, 64, 96 or 128 (32 and 96 run zero-padded to 64 and 128) */
+  int32_t head_dim;  /* a multiple of 32 up to 256, the reference's eight buckets (csrc/static_switch.h:
+                        50-77); kernels exist for 64, 128 and 256, the others run zero-padded on the
+                        next one up */
   float softmax_scale; /* > 0; P = exp(softmax_scale * (S - rowmax)) */
   int32_t is_causal;   /* 0/1; mask is lower-triangular including the diagonal (test.py:25-33) */
   int32_t v_layout;    /* FA8_V_TRANSPOSED or FA8_V_NATURAL */

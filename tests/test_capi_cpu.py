@@ -38,7 +38,9 @@ def test_error_strings_and_support_query():
     assert lib.fa8_supported(128, 64, _lib.FA8_V_TRANSPOSED) == _lib.FA8_OK
     assert lib.fa8_supported(128, 96, _lib.FA8_V_TRANSPOSED) == _lib.FA8_OK
     assert lib.fa8_supported(128, 32, _lib.FA8_V_NATURAL) == _lib.FA8_OK
+    assert lib.fa8_supported(128, 256, _lib.FA8_V_NATURAL) == _lib.FA8_OK
     assert lib.fa8_supported(128, 48, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
+    assert lib.fa8_supported(128, 288, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
     assert lib.fa8_supported(100, 64, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
     assert lib.fa8_supported(0, 64, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
 

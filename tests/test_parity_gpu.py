@@ -193,11 +193,12 @@ def test_different_query_and_key_lengths(Sq, Sk, causal):
     assert float((lse.cpu() - torch.logsumexp(s, dim=-1)).abs().max()) <= 2e-3
 
 
-@pytest.mark.parametrize("D", [32, 96])
+@pytest.mark.parametrize("D", [32, 96, 160, 192, 224, 256])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("layout", ["transposed", "natural"])
-def test_head_dims_of_the_reference_switch_below_128(D, causal, layout):
-    """Head dims 32 and 96 (csrc/static_switch.h:50-77) run as zero-padded 64 / 128."""
+def test_other_head_dims_of_the_reference_switch(D, causal, layout):
+    """The reference's head-dim buckets (csrc/static_switch.h:50-77) besides 64 and 128: 256 has
+    a kernel of its own (one query tile per CTA), the rest run zero-padded on the next one up."""
     d = dev()
     B, H, S = 1, 3, 640
     q8, k8, v8 = rand8(B, H, S, D, seed=D), rand8(B, H, S, D, seed=D + 1), rand8(B, H, S, D, seed=D + 2)
@@ -258,9 +259,10 @@ def test_operator_argument_errors_on_gpu():
         flash_attention_v2_cutlass(q.float(), q, vt, False, 0.125)
     with pytest.raises(RuntimeError, match="v must be"):
         flash_attention_v2_cutlass(q, q, q, False, 0.125)               # V not transposed
-    q48 = torch.zeros(1, 1, 128, 48, device=d).to(F8)
-    with pytest.raises(RuntimeError, match="unsupported"):
-        flash_attention_v2_cutlass(q48, q48, q48.transpose(2, 3).contiguous(), False, 0.125)
+    for bad_d in (48, 288):
+        qb = torch.zeros(1, 1, 128, bad_d, device=d).to(F8)
+        with pytest.raises(RuntimeError, match="unsupported"):
+            flash_attention_v2_cutlass(qb, qb, qb.transpose(2, 3).contiguous(), False, 0.125)
     with pytest.raises(RuntimeError, match="bad argument"):
         flash_attention_v2_cutlass(q, q, vt, False, 0.0)
     out = flash_attention_v2_cutlass(q, q, vt)                            # defaults: non-causal, scale 1
