@@ -32,14 +32,14 @@ DEFAULT_WORKLOAD = "mid_s4096_d128"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload, from the
 # ncu capture summarised under profiles/ (None until one has been taken).
 NCU_TRAFFIC_BYTES = {
-    # captured on mid_s4096_d128_b2 (64 slices): 100.72 MB read + 30.25 MB written (part of the
+    # captured on mid_s4096_d128_b2 (64 slices): 100.74 MB read + 30.30 MB written (part of the
     # fp16 output is still dirty in L2 at kernel end); traffic is proportional to the slice count,
     # the bench workload has 8x the slices
     "mid_s4096_d128_b2": 131.0e6,
     "mid_s4096_d128": 8 * 131.0e6,
-    "mid_s4096_d128_b2_causal": 128.9e6,
-    "mid_s4096_d128_causal": 8 * 128.9e6,
-    "prefill_s1024_d64": 128.7e6,
+    "mid_s4096_d128_b2_causal": 128.6e6,
+    "mid_s4096_d128_causal": 8 * 128.6e6,
+    "prefill_s1024_d64": 129.9e6,
 }
 
 
