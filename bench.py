@@ -340,7 +340,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_ms /= args.e2e_steps
-    h2d, d2h = runner.bytes_per_call(hq, hv)
+    h2d, d2h = runner.bytes_per_call(hq, hv, hk)
     e2e = {"value": w.flops(total_slices) / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world}
 

@@ -169,43 +169,97 @@ def quantize_e4m3(x: torch.Tensor, per_head: bool = False):
 
 
 class HostRunner:
-    """End-to-end call with HOST tensors: pinned host -> device copies, the kernel and
-    the device -> host copy of O all run on one stream; the call returns after O has
-    landed in (pinned) host memory.  Device and pinned buffers are allocated once per
-    shape and reused."""
+    """End-to-end call with HOST tensors: pinned host -> device copies, the kernel and the
+    device -> host copy of O.  The (batch, head) slices are independent, so the call is cut
+    into `chunks` groups of slices and pipelined over three streams: the upload of group
+    g+1, the kernel of group g and the download of group g-1 overlap, which uses both
+    directions of the host link at once.  The call returns after O has landed in (pinned)
+    host memory.  Device and pinned buffers are allocated once per shape and reused."""
 
-    def __init__(self, device: Optional[torch.device] = None):
+    def __init__(self, device: Optional[torch.device] = None, chunks: int = 16):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.chunks = max(1, int(chunks))
         self._key = None
+        self._streams = None
 
-    def _ensure(self, q: torch.Tensor, v: torch.Tensor):
-        key = (tuple(q.shape), tuple(v.shape))
+    def _ensure(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+        key = (tuple(q.shape), tuple(k.shape), tuple(v.shape), q.dtype)
         if key == self._key:
             return
         B, H, S, D = q.shape
         dev = self.device
-        self.dq = torch.empty(q.shape, dtype=torch.float8_e4m3fn, device=dev)
-        self.dk = torch.empty(q.shape, dtype=torch.float8_e4m3fn, device=dev)
-        self.dv = torch.empty(v.shape, dtype=torch.float8_e4m3fn, device=dev)
+        self.dq = torch.empty(q.shape, dtype=q.dtype, device=dev)
+        self.dk = torch.empty(k.shape, dtype=k.dtype, device=dev)
+        self.dv = torch.empty(v.shape, dtype=v.dtype, device=dev)
         self.do = torch.empty((B, H, S, D), dtype=torch.float16, device=dev)
         self.ho = torch.empty((B, H, S, D), dtype=torch.float16, pin_memory=True)
+        if self._streams is None:
+            self._streams = tuple(torch.cuda.Stream(device=dev) for _ in range(3))
         self._key = key
+
+    @staticmethod
+    def _groups(n: int, parts: int):
+        parts = min(parts, n)
+        return [(n * g // parts, n * (g + 1) // parts) for g in range(parts)]
 
     def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = False,
                  softmax_scale: float = 1.0, **kw) -> List[torch.Tensor]:
         for name, t in (("q", q), ("k", k), ("v", v)):
             if t.device.type != "cpu":
                 raise RuntimeError(f"{name} must be a host tensor")
-        self._ensure(q, v)
-        self.dq.copy_(q, non_blocking=True)
-        self.dk.copy_(k, non_blocking=True)
-        self.dv.copy_(v, non_blocking=True)
-        flash_attention_v2_cutlass(self.dq, self.dk, self.dv, is_causal, softmax_scale, out=self.do, **kw)
-        self.ho.copy_(self.do, non_blocking=True)
-        check_status(self.device)     # synchronises the stream
-        return [self.ho]
+            if t.dim() != 4 or not t.is_contiguous():
+                raise RuntimeError(f"{name} must be a contiguous 4-dimensional tensor")
+        if "out" in kw:
+            raise RuntimeError("HostRunner owns its output buffer; `out` is not accepted")
+        self._ensure(q, k, v)
+        B, H, Hk = q.shape[0], q.shape[1], k.shape[1]
+        per_head = any(kw.get(n) is not None and kw[n].numel() > 1 for n in ("descale_q", "descale_k", "descale_v"))
+        # A group is a contiguous range of every tensor: a range of the flattened (batch, head)
+        # axis when K and V have one head per query head, a range of batch entries otherwise.
+        # Row log-sum-exps and per-head descales are indexed by slice: one group then.
+        flat = (H == Hk)
+        if kw.get("return_lse") or per_head:
+            groups = [(0, B * H if flat else B)]
+        else:
+            groups = self._groups(B * H if flat else B, self.chunks)
+        if flat:
+            hq, hk, hv, dq, dk, dv, do, ho = (t.view(1, B * t.shape[1], t.shape[2], t.shape[3])
+                                              for t in (q, k, v, self.dq, self.dk, self.dv, self.do, self.ho))
+            cut = lambda t, a, b: t[:, a:b]
+        else:
+            hq, hk, hv, dq, dk, dv, do, ho = q, k, v, self.dq, self.dk, self.dv, self.do, self.ho
+            cut = lambda t, a, b: t[a:b]
+        s_in, s_run, s_out = self._streams
+        start = torch.cuda.Event()
+        start.record(torch.cuda.current_stream(self.device))
+        for st in self._streams:
+            st.wait_event(start)
+        extra = []
+        for (a, b) in groups:
+            with torch.cuda.stream(s_in):
+                cut(dq, a, b).copy_(cut(hq, a, b), non_blocking=True)
+                cut(dk, a, b).copy_(cut(hk, a, b), non_blocking=True)
+                cut(dv, a, b).copy_(cut(hv, a, b), non_blocking=True)
+                up = torch.cuda.Event()
+                up.record(s_in)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(up)
+                if len(groups) == 1:      # whole tensors in their own shape (lse and per-head descales follow it)
+                    extra = flash_attention_v2_cutlass(self.dq, self.dk, self.dv, is_causal, softmax_scale,
+                                                       out=self.do, **kw)[1:]
+                else:
+                    flash_attention_v2_cutlass(cut(dq, a, b), cut(dk, a, b), cut(dv, a, b), is_causal, softmax_scale,
+                                               out=cut(do, a, b), **kw)
+                ran = torch.cuda.Event()
+                ran.record(s_run)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ran)
+                cut(ho, a, b).copy_(cut(do, a, b), non_blocking=True)
+        s_out.synchronize()
+        check_status(self.device)
+        return [self.ho] + [t.cpu() for t in extra]
 
-    def bytes_per_call(self, q: torch.Tensor, v: torch.Tensor):
-        h2d = 2 * q.numel() + v.numel()
+    def bytes_per_call(self, q: torch.Tensor, v: torch.Tensor, k: Optional[torch.Tensor] = None):
+        h2d = q.numel() + (q.numel() if k is None else k.numel()) + v.numel()
         d2h = 2 * q.numel()
         return h2d, d2h

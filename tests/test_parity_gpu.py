@@ -321,3 +321,24 @@ def test_box_scale_config_shape():
     out = flash_attention_v2_cutlass(q8.view(1, n, S, D), k8.view(1, n, S, D), vt8.view(1, n, D, S), True, scale)[0][0]
     check_status(d)
     _sampled_rows_check(q8, k8, vt8, out, [0, 1023, n - 1], True, scale, n_rows=128)
+
+
+@pytest.mark.parametrize("Hk,layout,lse", [(6, "transposed", False), (6, "natural", True), (2, "natural", False)])
+def test_host_runner_pipelines_groups_of_slices(Hk, layout, lse):
+    """Host tensors in, host tensor out: upload, kernel and download of slice groups overlap on three
+    streams; the result is bitwise the one the operator gives on device tensors."""
+    from cutlass_flash_atten_fp8_b200 import HostRunner
+    d = dev()
+    B, H, S, D = 3, 6, 384, 64
+    q8, k8, v8 = rand8(B, H, S, D, seed=1), rand8(B, Hk, S, D, seed=2), rand8(B, Hk, S, D, seed=3)
+    v_host = (v8 if layout == "natural" else v8.transpose(2, 3).contiguous())
+    pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
+    runner = HostRunner(d, chunks=4)
+    got = runner(pin(q8), pin(k8), pin(v_host), True, 0.125, v_layout=layout, return_lse=lse)
+    want = flash_attention_v2_cutlass(q8.to(d), k8.to(d), v_host.to(d), True, 0.125, v_layout=layout, return_lse=lse)
+    check_status(d)
+    assert got[0].device.type == "cpu" and torch.equal(got[0], want[0].cpu())
+    if lse:
+        assert torch.equal(got[1], want[1].cpu())
+    again = runner(pin(q8), pin(k8), pin(v_host), True, 0.125, v_layout=layout)[0]     # buffers reused
+    assert torch.equal(again, want[0].cpu())
