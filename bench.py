@@ -314,6 +314,26 @@ def main():
     tflops = w.flops(total_slices) / ms_step / 1e9
     tflops_gpu = tflops / world
 
+    # Power settles over seconds on a 1 kW part: the same launch back to back for at least two
+    # seconds, reported beside the K-step figure (rank 0 of a single-GPU run only).
+    sustained = None
+    if world == 1 and not args.kernel_only:
+        n_sus = max(args.steps, int(2000.0 / ms_step) + 1)
+        sampler2 = ClockSampler(local_rank)
+        torch.cuda.synchronize()
+        sampler2.start()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(n_sus):
+            step()
+        s1.record()
+        torch.cuda.synchronize()
+        clocks2 = sampler2.stop()
+        check_status(device)
+        ms_sus = s0.elapsed_time(s1) / n_sus
+        sustained = {"steps": n_sus, "ms_per_step": ms_sus, "value": w.flops(total_slices) / ms_sus / 1e9,
+                     "unit": "TFLOP/s", "clocks": clocks2}
+
     if args.kernel_only:
         if rank == 0:
             print(json.dumps({"metric": "fp8_attn_fwd_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
@@ -382,6 +402,8 @@ def main():
         }
         if gather_ms is not None:
             line["gather_o_ms"] = gather_ms
+        if sustained is not None:
+            line["sustained"] = sustained
         if world == 1:
             line["quantize_prepass"] = quantize_rate(device, peaks)
             line["reference_kernel"] = (reference_kernel_tflops(w, q4, k4, v4, args.steps) if not natural

@@ -51,3 +51,11 @@ def test_workload_arithmetic():
     assert w.hbm_bytes() == pytest.approx(1.342e9, rel=1e-3)
     assert synth.WORKLOADS["mid_s4096_d128_causal"].flops() == pytest.approx(2.199e12, rel=1e-3)
     assert synth.WORKLOADS["box_s8192_d128_causal"].flops() == pytest.approx(3.518e13, rel=1e-3)
+
+
+@pytest.mark.parametrize("n,parts", [(512, 16), (18, 4), (3, 16), (1, 8), (7, 7)])
+def test_host_runner_groups_partition_the_slices(n, parts):
+    from cutlass_flash_atten_fp8_b200 import HostRunner
+    g = HostRunner._groups(n, parts)
+    assert len(g) == min(n, parts) and g[0][0] == 0 and g[-1][1] == n
+    assert all(b == c for (_, b), (c, _) in zip(g, g[1:])) and all(b > a for a, b in g)
