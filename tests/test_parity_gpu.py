@@ -342,3 +342,33 @@ def test_host_runner_pipelines_groups_of_slices(Hk, layout, lse):
         assert torch.equal(got[1], want[1].cpu())
     again = runner(pin(q8), pin(k8), pin(v_host), True, 0.125, v_layout=layout)[0]     # buffers reused
     assert torch.equal(again, want[0].cpu())
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_very_long_sequence(causal):
+    """One head of 65 536 positions (256 tile pairs, 1 024 sub-blocks per work item): sampled rows."""
+    d = dev()
+    S, D = 65536, 128
+    g = torch.Generator(device=d).manual_seed(9)
+    q8, k8 = (torch.randn(2, S, D, generator=g, device=d).to(F8) for _ in range(2))
+    vt8 = torch.randn(2, D, S, generator=g, device=d).to(F8)
+    scale = 1 / math.sqrt(D)
+    out = flash_attention_v2_cutlass(q8.view(1, 2, S, D), k8.view(1, 2, S, D), vt8.view(1, 2, D, S), causal, scale)[0][0]
+    check_status(d)
+    assert not torch.isnan(out).any()
+    _sampled_rows_check(q8, k8, vt8, out, [1], causal, scale, n_rows=96)
+
+
+def test_many_short_slices():
+    """8 192 (batch, head) slices of one tile each: the unit index runs far past the grid size."""
+    d = dev()
+    n, S, D = 8192, 128, 64
+    g = torch.Generator(device=d).manual_seed(10)
+    q8, k8, v8 = (torch.randn(n, S, D, generator=g, device=d).to(F8) for _ in range(3))
+    out = flash_attention_v2_cutlass(q8.view(64, 128, S, D), k8.view(64, 128, S, D), v8.view(64, 128, S, D), True, 0.125,
+                                     v_layout="natural")[0].view(n, S, D)
+    check_status(d)
+    for s in (0, 4097, n - 1):
+        ref = attention_fp32(q8[s].cpu().view(1, 1, S, D), k8[s].cpu().view(1, 1, S, D), v8[s].cpu().view(1, 1, S, D), True, 0.125)[0, 0]
+        m = error_metrics(out[s], ref)
+        assert m["rel_l2"] <= REL_L2_FP32 and m["max_abs"] <= MAX_ABS_FRAC_FP32 * m["max_ref"], (s, m)
