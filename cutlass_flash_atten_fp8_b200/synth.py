@@ -57,6 +57,8 @@ WORKLOADS: Dict[str, Workload] = {
     # batch-2 cuts of the mid-length shape: small enough for a multi-pass profiler capture, still larger than L2
     "mid_s4096_d128_b2": Workload("mid_s4096_d128_b2", 2, 32, 4096, 128, False, outliers=True, seed=1003),
     "mid_s4096_d128_b2_causal": Workload("mid_s4096_d128_b2_causal", 2, 32, 4096, 128, True, outliers=True, seed=1003),
+    # head_dim 256 (one query tile per CTA), sized like the batch-2 cuts
+    "mid_s4096_d256_b2": Workload("mid_s4096_d256_b2", 2, 16, 4096, 256, False, outliers=True, seed=1006),
     "long_s16384_d128_causal": Workload("long_s16384_d128_causal", 1, 32, 16384, 128, True, seed=1004),
     "box_s8192_d128_causal": Workload("box_s8192_d128_causal", 64, 32, 8192, 128, True, seed=1005),
 }
