@@ -8,7 +8,7 @@ from __future__ import annotations
 import ctypes
 import os
 
-from .build import LIB_PATH
+from .build import LIB_PATH, is_stale
 
 FA8_OK = 0
 FA8_ERR_BAD_ARG = -1
@@ -54,6 +54,10 @@ def load() -> ctypes.CDLL:
         raise ImportError(
             f"{LIB_PATH} is missing: build it with `python -m cutlass_flash_atten_fp8_b200.build` "
             "(there is no CPU or eager fallback)")
+    if is_stale():
+        raise ImportError(
+            f"{LIB_PATH} is older than its sources: rebuild it with "
+            "`python -m cutlass_flash_atten_fp8_b200.build` (a stale binary is never loaded silently)")
     lib = ctypes.CDLL(LIB_PATH)
     lib.fa8_fwd.argtypes = [ctypes.POINTER(Fa8FwdParams), ctypes.c_void_p]
     lib.fa8_fwd.restype = ctypes.c_int

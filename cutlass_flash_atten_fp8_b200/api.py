@@ -35,14 +35,14 @@ def status_word(device: torch.device) -> torch.Tensor:
     return _status_words[idx]
 
 
-def check_status(device: Optional[torch.device] = None) -> None:
+def check_status(device: Optional[torch.device] = None, word: Optional[torch.Tensor] = None) -> None:
     """Synchronises the current stream of `device` and raises RuntimeError if a kernel
     launched through this module reported an expired wait (or the stream is in error).
     Stands where the reference has cudaDeviceSynchronize + CUDA_ERROR_CHECK
     (csrc/flash_attention.cu:663-665), but raises instead of exiting the process."""
     lib = _lib.load()
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-    word = status_word(device)
+    word = status_word(device) if word is None else word
     code = ctypes.c_int32(0)
     with torch.cuda.device(word.device):
         stream = torch.cuda.current_stream(word.device).cuda_stream
@@ -59,7 +59,8 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
                                return_lse: bool = False,
                                descale_q: Optional[torch.Tensor] = None,
                                descale_k: Optional[torch.Tensor] = None,
-                               descale_v: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
+                               descale_v: Optional[torch.Tensor] = None,
+                               _status: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
     """FP8 attention forward.
 
     q, k: float8_e4m3fn (or, all three, float8_e5m2: the reference's FP8_SWITCH,
@@ -125,7 +126,7 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
         q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=out.data_ptr(),
         batch=B, heads=H, seqlen=S, head_dim=D, softmax_scale=float(softmax_scale),
         is_causal=int(bool(is_causal)), v_layout=layout, o_scale=float(o_scale),
-        status_word=status_word(q.device).data_ptr(),
+        status_word=(_status if _status is not None else status_word(q.device)).data_ptr(),
         softmax_lse=(lse.data_ptr() if lse is not None else None), heads_kv=Hk,
         descale_q=(descale_q.data_ptr() if descale_q is not None else None),
         descale_k=(descale_k.data_ptr() if descale_k is not None else None),
@@ -135,6 +136,10 @@ def flash_attention_v2_cutlass(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     with torch.cuda.device(q.device):
         rc = lib.fa8_fwd(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
     if rc != _lib.FA8_OK:
+        # FA8_ERR_DEVICE_TIMEOUT here means an EARLIER launch on this device failed (the library
+        # learns of it through a host-visible flag); it has cleared the status words and did not
+        # enqueue this call.  The reference would have exited the process at that launch
+        # (include/attention_api.cuh:20-29).
         raise RuntimeError(_lib.error_message(rc))
     return [out, lse] if return_lse else [out]
 
@@ -150,14 +155,14 @@ def quantize_e4m3(x: torch.Tensor, per_head: bool = False):
     if x.dtype not in (torch.float16, torch.bfloat16):
         raise RuntimeError(f"x must be float16 or bfloat16, got {x.dtype}")
     dt = _lib.FA8_DTYPE_BF16 if x.dtype == torch.bfloat16 else _lib.FA8_DTYPE_FP16
+    if per_head and x.dim() < 3:
+        raise RuntimeError("per_head needs a [batch, heads, ...] tensor")
     x8 = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
     n_seg = x.shape[0] * x.shape[1] if per_head else 1
     scal = torch.empty(2 * n_seg, dtype=torch.float32, device=x.device)       # [amax..., descale...]
     with torch.cuda.device(x.device):
         stream = torch.cuda.current_stream(x.device).cuda_stream
         if per_head:
-            if x.dim() < 3:
-                raise RuntimeError("per_head needs a [batch, heads, ...] tensor")
             rc = lib.fa8_quantize_e4m3_segments(x.data_ptr(), dt, x8.data_ptr(), x.numel() // n_seg, n_seg,
                                                 scal.data_ptr(), scal.data_ptr() + 4 * n_seg, stream)
         else:
@@ -173,14 +178,22 @@ class HostRunner:
     device -> host copy of O.  The (batch, head) slices are independent, so the call is cut
     into `chunks` groups of slices and pipelined over three streams: the upload of group
     g+1, the kernel of group g and the download of group g-1 overlap, which uses both
-    directions of the host link at once.  The call returns after O has landed in (pinned)
-    host memory.  Device and pinned buffers are allocated once per shape and reused."""
+    directions of the host link at once.  The call returns after O has landed in pinned host
+    memory: a tensor of its own for every call (torch's pinned-memory cache makes that cheap
+    once an earlier result has been released), or the caller's `out=` (fp16, shaped like q;
+    pinned if the download is to overlap).  Device buffers are allocated once per shape and
+    reused.  Each runner has its own device status word."""
 
-    def __init__(self, device: Optional[torch.device] = None, chunks: int = 16):
+    def __init__(self, device: Optional[torch.device] = None, chunks: int = 16, timing: bool = False):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.chunks = max(1, int(chunks))
+        # timing=True brackets every copy group and kernel with CUDA events and leaves the busy
+        # time of each stage of the last call in `last_timing` (milliseconds, summed over groups)
+        self.timing = bool(timing)
+        self.last_timing = None
         self._key = None
         self._streams = None
+        self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     def _ensure(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
         key = (tuple(q.shape), tuple(k.shape), tuple(v.shape), q.dtype)
@@ -192,7 +205,6 @@ class HostRunner:
         self.dk = torch.empty(k.shape, dtype=k.dtype, device=dev)
         self.dv = torch.empty(v.shape, dtype=v.dtype, device=dev)
         self.do = torch.empty((B, H, S, D), dtype=torch.float16, device=dev)
-        self.ho = torch.empty((B, H, S, D), dtype=torch.float16, pin_memory=True)
         if self._streams is None:
             self._streams = tuple(torch.cuda.Stream(device=dev) for _ in range(3))
         self._key = key
@@ -209,9 +221,13 @@ class HostRunner:
                 raise RuntimeError(f"{name} must be a host tensor")
             if t.dim() != 4 or not t.is_contiguous():
                 raise RuntimeError(f"{name} must be a contiguous 4-dimensional tensor")
-        if "out" in kw:
-            raise RuntimeError("HostRunner owns its output buffer; `out` is not accepted")
         self._ensure(q, k, v)
+        host_out = kw.pop("out", None)
+        if host_out is None:
+            host_out = torch.empty(self.do.shape, dtype=torch.float16, pin_memory=True)
+        elif (host_out.device.type != "cpu" or host_out.dtype != torch.float16 or not host_out.is_contiguous()
+              or tuple(host_out.shape) != tuple(self.do.shape)):
+            raise RuntimeError("out must be a contiguous float16 host tensor shaped like q")
         B, H, Hk = q.shape[0], q.shape[1], k.shape[1]
         per_head = any(kw.get(n) is not None and kw[n].numel() > 1 for n in ("descale_q", "descale_k", "descale_v"))
         # A group is a contiguous range of every tensor: a range of the flattened (batch, head)
@@ -224,10 +240,10 @@ class HostRunner:
             groups = self._groups(B * H if flat else B, self.chunks)
         if flat:
             hq, hk, hv, dq, dk, dv, do, ho = (t.view(1, B * t.shape[1], t.shape[2], t.shape[3])
-                                              for t in (q, k, v, self.dq, self.dk, self.dv, self.do, self.ho))
+                                              for t in (q, k, v, self.dq, self.dk, self.dv, self.do, host_out))
             cut = lambda t, a, b: t[:, a:b]
         else:
-            hq, hk, hv, dq, dk, dv, do, ho = q, k, v, self.dq, self.dk, self.dv, self.do, self.ho
+            hq, hk, hv, dq, dk, dv, do, ho = q, k, v, self.dq, self.dk, self.dv, self.do, host_out
             cut = lambda t, a, b: t[a:b]
         s_in, s_run, s_out = self._streams
         start = torch.cuda.Event()
@@ -235,29 +251,46 @@ class HostRunner:
         for st in self._streams:
             st.wait_event(start)
         extra = []
+        marks = {"h2d": [], "kernel": [], "d2h": []}
+
+        def mark(stage, stream):
+            if self.timing:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(stream)
+                marks[stage].append(ev)
+
         for (a, b) in groups:
             with torch.cuda.stream(s_in):
+                mark("h2d", s_in)
                 cut(dq, a, b).copy_(cut(hq, a, b), non_blocking=True)
                 cut(dk, a, b).copy_(cut(hk, a, b), non_blocking=True)
                 cut(dv, a, b).copy_(cut(hv, a, b), non_blocking=True)
+                mark("h2d", s_in)
                 up = torch.cuda.Event()
                 up.record(s_in)
             with torch.cuda.stream(s_run):
                 s_run.wait_event(up)
+                mark("kernel", s_run)
                 if len(groups) == 1:      # whole tensors in their own shape (lse and per-head descales follow it)
                     extra = flash_attention_v2_cutlass(self.dq, self.dk, self.dv, is_causal, softmax_scale,
-                                                       out=self.do, **kw)[1:]
+                                                       out=self.do, _status=self._status, **kw)[1:]
                 else:
                     flash_attention_v2_cutlass(cut(dq, a, b), cut(dk, a, b), cut(dv, a, b), is_causal, softmax_scale,
-                                               out=cut(do, a, b), **kw)
+                                               out=cut(do, a, b), _status=self._status, **kw)
+                mark("kernel", s_run)
                 ran = torch.cuda.Event()
                 ran.record(s_run)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ran)
+                mark("d2h", s_out)
                 cut(ho, a, b).copy_(cut(do, a, b), non_blocking=True)
+                mark("d2h", s_out)
         s_out.synchronize()
-        check_status(self.device)
-        return [self.ho] + [t.cpu() for t in extra]
+        if self.timing:
+            self.last_timing = {st: sum(ev[i].elapsed_time(ev[i + 1]) for i in range(0, len(ev), 2))
+                                for st, ev in marks.items()}
+        check_status(self.device, word=self._status)
+        return [host_out] + [t.cpu() for t in extra]
 
     def bytes_per_call(self, q: torch.Tensor, v: torch.Tensor, k: Optional[torch.Tensor] = None):
         h2d = q.numel() + (q.numel() if k is None else k.numel()) + v.numel()

@@ -70,29 +70,94 @@ bool make_map_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t mi
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// The library's own status word, one per device that loads the module: used when the caller
+// passes none, so that an expired wait is never lost.
+__device__ int g_status_word;
+
+// Per-device state, set up by the first call on that device:
+//   dev_word   address of g_status_word on the device;
+//   host_flag  one int of mapped, pinned host memory that a kernel stores its code into when
+//              a bounded wait runs out (whatever status word the launch was given).  The host
+//              reads it at the start of every later call: a failed launch is then reported by
+//              the next call at the latest, with no copy and no synchronisation in between.
+struct DeviceState {
+  std::once_flag once;
+  bool ok = false;
+  int* dev_word = nullptr;
+  volatile int* host_flag = nullptr;
+  int* host_flag_dev = nullptr;
+};
+constexpr int kMaxDevices = 64;
+DeviceState g_dev[kMaxDevices];
+
+DeviceState* device_state() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  DeviceState& st = g_dev[dev];
+  std::call_once(st.once, [&st] {
+    void* word = nullptr;
+    void* host = nullptr;
+    void* host_dev = nullptr;
+    if (cudaGetSymbolAddress(&word, g_status_word) != cudaSuccess) return;    // zero at module load
+    if (cudaHostAlloc(&host, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) return;
+    *static_cast<volatile int*>(host) = 0;
+    if (cudaHostGetDevicePointer(&host_dev, host, 0) != cudaSuccess) {
+      cudaFreeHost(host);
+      return;
+    }
+    st.dev_word = static_cast<int*>(word);
+    st.host_flag = static_cast<volatile int*>(host);
+    st.host_flag_dev = static_cast<int*>(host_dev);
+    st.ok = true;
+  });
+  if (!st.ok) {
+    cudaGetLastError();     // the failure is reported by the caller as "no state", not left pending
+    return nullptr;
+  }
+  return &st;
+}
+
+// Collects a failure an earlier launch on this device left in the host flag: clears the flag
+// and, stream-ordered, the device words, and returns the code (0 = none).
+int collect_earlier_failure(DeviceState* st, int32_t* caller_word, cudaStream_t stream) {
+  if (!st) return 0;
+  const int code = *st->host_flag;
+  if (code == 0) return 0;
+  *st->host_flag = 0;
+  cudaMemsetAsync(st->dev_word, 0, sizeof(int), stream);
+  if (caller_word) cudaMemsetAsync(caller_word, 0, sizeof(int), stream);
+  return code;
+}
+
 }  // namespace
 
 extern "C" {
 
-int fa8_version(void) { return 106; }
+int fa8_version(void) { return 107; }
 
 const char* fa8_error_string(int code) {
   switch (code) {
     case FA8_OK: return "ok";
     case FA8_ERR_BAD_ARG: return "bad argument (null or misaligned pointer, non-positive size or scale)";
-    case FA8_ERR_UNSUPPORTED: return "unsupported shape or layout (head_dim must be 64 or 128, seqlen a multiple of 16)";
+    case FA8_ERR_UNSUPPORTED:
+      return "unsupported shape or layout (head_dim must be a multiple of 32 up to 256; with V transposed the "
+             "key/value length must be a multiple of 16)";
     case FA8_ERR_CUDA: return "CUDA call failed";
-    case FA8_ERR_DEVICE_TIMEOUT: return "a bounded wait inside the kernel expired";
+    case FA8_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
     default: return "unknown fa8 status";
   }
 }
 
 const char* fa8_last_error_detail(void) { return g_detail; }
 
-int fa8_supported(int32_t seqlen, int32_t head_dim, int32_t v_layout) {
+int fa8_supported(int32_t seqlen_k, int32_t head_dim, int32_t v_layout) {
   if (head_dim < 32 || head_dim > 256 || (head_dim % 32) != 0) return FA8_ERR_UNSUPPORTED;
-  if (seqlen <= 0 || (seqlen % 16) != 0) return FA8_ERR_UNSUPPORTED;
   if (v_layout != FA8_V_TRANSPOSED && v_layout != FA8_V_NATURAL) return FA8_ERR_UNSUPPORTED;
+  if (seqlen_k <= 0) return FA8_ERR_UNSUPPORTED;
+  // Only V^T has the sequence as its contiguous axis: a row of it is seqlen_k bytes long, and
+  // the copy engine wants row strides in multiples of 16 bytes.  Rows of Q, K and natural V are
+  // head_dim bytes, so their sequence lengths are free.
+  if (v_layout == FA8_V_TRANSPOSED && (seqlen_k % 16) != 0) return FA8_ERR_UNSUPPORTED;
   return FA8_OK;
 }
 
@@ -109,16 +174,25 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
        reinterpret_cast<uintptr_t>(p->descale_v)) & 3u) return FA8_ERR_BAD_ARG;
   if (p->v_layout != FA8_V_TRANSPOSED && p->v_layout != FA8_V_NATURAL) return FA8_ERR_BAD_ARG;
   if (p->fp8_format != FA8_FP8_E4M3 && p->fp8_format != FA8_FP8_E5M2) return FA8_ERR_BAD_ARG;
-  int sup = fa8_supported(p->seqlen, p->head_dim, p->v_layout);
+  if (p->seqlen_k < 0) return FA8_ERR_BAD_ARG;
+  const int32_t seqlen_k = p->seqlen_k > 0 ? p->seqlen_k : p->seqlen;
+  int sup = fa8_supported(seqlen_k, p->head_dim, p->v_layout);
   if (sup != FA8_OK) return sup;
   const int64_t bh = static_cast<int64_t>(p->batch) * p->heads;
   const int32_t heads_kv = p->heads_kv > 0 ? p->heads_kv : p->heads;
   if (heads_kv > p->heads || p->heads % heads_kv != 0) return FA8_ERR_BAD_ARG;
   const int64_t bh_kv = static_cast<int64_t>(p->batch) * heads_kv;
 
-  const int32_t seqlen_k = p->seqlen_k > 0 ? p->seqlen_k : p->seqlen;
-  if (p->seqlen_k < 0) return FA8_ERR_BAD_ARG;
-  if (fa8_supported(seqlen_k, p->head_dim, p->v_layout) != FA8_OK) return FA8_ERR_UNSUPPORTED;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // A launch that went wrong earlier on this device is reported now, before anything new is
+  // enqueued (the reference's only error path is exit(), include/attention_api.cuh:20-29).
+  DeviceState* dstate = device_state();
+  if (const int code = collect_earlier_failure(dstate, p->status_word, stream)) {
+    char buf[96];
+    std::snprintf(buf, sizeof(buf), "device code 0x%x; this call was not enqueued", code);
+    set_detail("an earlier launch on this device reported an expired wait", buf);
+    return FA8_ERR_DEVICE_TIMEOUT;
+  }
   const uint64_t S = static_cast<uint64_t>(p->seqlen), D = static_cast<uint64_t>(p->head_dim);
   const uint64_t Sk = static_cast<uint64_t>(seqlen_k);
   // The kernel is built for head dims 64, 128 and 256 (the reference's switch has eight
@@ -147,7 +221,8 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   args.head_dim = p->head_dim;
   args.scale_log2 = p->softmax_scale * 1.4426950408889634f;
   args.o_scale = p->o_scale;
-  args.status = p->status_word;
+  args.status = p->status_word ? p->status_word : (dstate ? dstate->dev_word : nullptr);
+  args.host_status = dstate ? dstate->host_flag_dev : nullptr;
   args.lse = p->softmax_lse;
   args.descale_q = p->descale_q;
   args.descale_k = p->descale_k;
@@ -164,8 +239,7 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   if (bh * per_slice > 0x7fffffff) return FA8_ERR_UNSUPPORTED;
   args.n_units = static_cast<int>(bh * per_slice);
   cudaError_t e = fa8::launch_fwd(static_cast<int>(d_box), p->is_causal != 0, p->v_layout == FA8_V_NATURAL,
-                                  p->fp8_format == FA8_FP8_E5M2, tq, tk, tv, args,
-                                  static_cast<cudaStream_t>(cuda_stream));
+                                  p->fp8_format == FA8_FP8_E5M2, tq, tk, tv, args, stream);
   if (e != cudaSuccess) {
     set_detail("kernel launch", cudaGetErrorString(e));
     return FA8_ERR_CUDA;
@@ -207,9 +281,13 @@ int fa8_quantize_e4m3_segments(const void* src, int32_t src_dtype, void* dst, in
 
 int fa8_selftest_expired_wait(int32_t* status_word, uint32_t limit_us, void* cuda_stream) {
   g_detail[0] = '\0';
-  if (!status_word || (reinterpret_cast<uintptr_t>(status_word) & 3u)) return FA8_ERR_BAD_ARG;
+  if (reinterpret_cast<uintptr_t>(status_word) & 3u) return FA8_ERR_BAD_ARG;
   if (limit_us == 0 || limit_us > 1000000u) return FA8_ERR_BAD_ARG;     // at most one second
-  cudaError_t e = fa8::launch_expired_wait(status_word, 1000ull * limit_us, static_cast<cudaStream_t>(cuda_stream));
+  DeviceState* dstate = device_state();
+  if (!status_word && !dstate) return FA8_ERR_BAD_ARG;
+  cudaError_t e = fa8::launch_expired_wait(status_word ? status_word : dstate->dev_word,
+                                           dstate ? dstate->host_flag_dev : nullptr, 1000ull * limit_us,
+                                           static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess) {
     set_detail("kernel launch", cudaGetErrorString(e));
     return FA8_ERR_CUDA;
@@ -219,14 +297,29 @@ int fa8_selftest_expired_wait(int32_t* status_word, uint32_t limit_us, void* cud
 
 int fa8_check_status(const int32_t* status_word, void* cuda_stream, int32_t* code_out) {
   g_detail[0] = '\0';
-  if (!status_word) return FA8_ERR_BAD_ARG;
+  DeviceState* dstate = device_state();
+  const int32_t* word = status_word ? status_word : (dstate ? dstate->dev_word : nullptr);
+  if (!word) return FA8_ERR_BAD_ARG;
   int32_t host = 0;
   cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
-  cudaError_t e = cudaMemcpyAsync(&host, status_word, sizeof(host), cudaMemcpyDeviceToHost, st);
+  cudaError_t e = cudaMemcpyAsync(&host, word, sizeof(host), cudaMemcpyDeviceToHost, st);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) {
     set_detail("status read-back", cudaGetErrorString(e));
     return FA8_ERR_CUDA;
+  }
+  if (host != 0 && dstate) {
+    // Reported here: the next fa8_fwd need not report it again.  The library's own word is
+    // cleared as well; a caller's word is the caller's to clear.
+    *dstate->host_flag = 0;
+    if (!status_word) {
+      e = cudaMemsetAsync(dstate->dev_word, 0, sizeof(int), st);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+      if (e != cudaSuccess) {
+        set_detail("status reset", cudaGetErrorString(e));
+        return FA8_ERR_CUDA;
+      }
+    }
   }
   if (code_out) *code_out = host;
   return host == 0 ? FA8_OK : FA8_ERR_DEVICE_TIMEOUT;

@@ -30,7 +30,9 @@ struct KernelArgs {
   int descale_per_head;           // the three are arrays: [batch*heads] for Q, [batch*heads_kv] for K, V
   float* lse;                     // optional [batch*heads, seqlen] fp32: log-sum-exp of the scaled scores
   float softmax_scale;            // as given by the caller (natural-log units, for lse)
-  int* status;                    // optional device word; non-zero after a bounded wait expired
+  int* status;                    // device word; non-zero after a bounded wait expired (later CTAs then return at once)
+  int* host_status;               // optional word in mapped host memory: receives the same code, so that
+                                  // the host learns of it without a copy or a synchronisation
   unsigned long long timeout_ns;  // bound of every mbarrier wait
 };
 
@@ -43,7 +45,7 @@ cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, con
                        cudaStream_t stream);
 
 // One warp waits (bounded by limit_ns) on a barrier that never completes; see fa8_selftest_expired_wait.
-cudaError_t launch_expired_wait(int* status, unsigned long long limit_ns, cudaStream_t stream);
+cudaError_t launch_expired_wait(int* status, int* host_status, unsigned long long limit_ns, cudaStream_t stream);
 
 // Amax quantisation fp16/bf16 -> e4m3 (fa8_quant.cu) of n_seg contiguous segments of n
 // elements each: amax[s] = max|src_s|, dst_s = e4m3(src_s * 448 / amax[s]),

@@ -66,7 +66,10 @@ __global__ void __launch_bounds__(kQuantThreads) amax_kernel(const uint4* __rest
     m = threadIdx.x < kQuantThreads / 32 ? part[threadIdx.x] : 0.f;
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    // non-negative floats order like their bit patterns; NaN inputs propagate as a large pattern
+    // Non-negative floats order like their bit patterns.  fmaxf drops NaN inputs, so a NaN does
+    // not reach amax (it still casts to the fp8 NaN in pass 2); an infinite input makes amax
+    // infinite, the scale 448/inf = 0 and every finite output 0 (inf * 0 = NaN for the infinite
+    // ones): inputs are expected to be finite.
     if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));
   }
 }

@@ -39,28 +39,34 @@ def global_amax(local_amax: torch.Tensor, group=None) -> torch.Tensor:
 
 def gather_output(o_local: torch.Tensor, n_slices: int, dst: int = 0, group=None) -> Optional[torch.Tensor]:
     """Optional gather of the per-rank O slices ([n_local, seqlen, head_dim]) on rank
-    `dst` in flattened (batch*heads) order.  Returns the full tensor on dst, else None."""
+    `dst` in flattened (batch*heads) order.  Returns the full tensor on dst, else None.
+    `dst` and the shard order are ranks WITHIN `group` (the default group: global ranks)."""
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
         return o_local
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     ranges = all_ranges(n_slices, world)
+    # torch's point-to-point and gather calls name peers by GLOBAL rank, whatever the group
+
+    def glob(r: int) -> int:
+        return r if group is None else dist.get_global_rank(group, r)
+
     if rank == dst:
         full = torch.empty((n_slices,) + tuple(o_local.shape[1:]), dtype=o_local.dtype, device=o_local.device)
         parts = [full[lo:hi] for lo, hi in ranges]
         if len({hi - lo for lo, hi in ranges}) == 1:
-            dist.gather(o_local, gather_list=parts, dst=dst, group=group)
+            dist.gather(o_local, gather_list=parts, dst=glob(dst), group=group)
         else:
             reqs = []
             for r, (lo, hi) in enumerate(ranges):
                 if r == dst:
                     parts[r].copy_(o_local)
                 elif hi > lo:
-                    reqs.append(dist.irecv(parts[r], src=r, group=group))
+                    reqs.append(dist.irecv(parts[r], src=glob(r), group=group))
             for q in reqs:
                 q.wait()
         return full
     if len({hi - lo for lo, hi in ranges}) == 1:
-        dist.gather(o_local, gather_list=None, dst=dst, group=group)
+        dist.gather(o_local, gather_list=None, dst=glob(dst), group=group)
     elif o_local.shape[0] > 0:
-        dist.send(o_local, dst=dst, group=group)
+        dist.send(o_local, dst=glob(dst), group=group)
     return None

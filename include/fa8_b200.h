@@ -54,7 +54,9 @@ typedef struct fa8_fwd_params {
   void* o;         /* fp16 [batch, heads, seqlen, head_dim], written by the call */
   int32_t batch;
   int32_t heads;
-  int32_t seqlen;    /* query rows per head (and key rows unless seqlen_k says otherwise); multiple of 16 */
+  int32_t seqlen;    /* query rows per head (and key rows unless seqlen_k says otherwise); any positive
+                        length, except that the key/value length must be a multiple of 16 when V is
+                        passed transposed (its rows are then that many bytes long) */
   int32_t head_dim;  /* a multiple of 32 up to 256, the reference's eight buckets (csrc/static_switch.h:
                         50-77); kernels exist for 64, 128 and 256, the others run zero-padded on the
                         next one up */
@@ -65,7 +67,10 @@ typedef struct fa8_fwd_params {
                           per-tensor scaled inputs folds V's descale here and Q's and K's into
                           softmax_scale */
   int32_t* status_word; /* optional device int32, zero before the call; the kernel stores a
-                           non-zero code there if one of its bounded waits runs out */
+                           non-zero code there if one of its bounded waits runs out, and CTAs that
+                           find it non-zero return without writing O.  NULL = a word the library
+                           keeps per device.  Either way the failure also reaches the host through
+                           a flag of the library's own, see fa8_fwd. */
   float* softmax_lse;   /* optional device fp32 [batch, heads, seqlen]: log(sum_j exp(softmax_scale *
                            s_ij)) per query row, written when not NULL.  The reference carries the
                            pointer (softmax_lse_ptr, csrc/flash.h:56) but never fills it
@@ -84,7 +89,8 @@ typedef struct fa8_fwd_params {
                            re-quantised to the same format.  The reference switches on the input dtype
                            the same way (FP8_SWITCH, csrc/flash_attention.cu:308,631). */
   int32_t seqlen_k;     /* rows of K and V per head when they differ from `seqlen` (cross attention,
-                           a prompt attending to a longer cache); 0 = seqlen.  Multiple of 16.  The
+                           a prompt attending to a longer cache); 0 = seqlen.  A multiple of 16 when V
+                           is transposed, otherwise any positive length.  The
                            causal mask stays aligned top-left (key index <= query index), as in the
                            reference (csrc/flash_attention.cu:24-71); the reference carries q_seqlen and
                            k_seqlen separately (csrc/flash.h) but its test only runs them equal. */
@@ -95,11 +101,22 @@ typedef struct fa8_fwd_params {
 
 /* Enqueues the forward on `cuda_stream` (a cudaStream_t; NULL = default stream)
  * of the current device.  Returns FA8_OK when the launch was accepted.  Replaces
- * flash_attention_v2_cutlass (csrc/flash_attention.cu:639-668). */
+ * flash_attention_v2_cutlass (csrc/flash_attention.cu:639-668).
+ *
+ * Failure reporting without a synchronisation: a kernel whose bounded wait ran out also stores
+ * its code in a word of pinned host memory the library owns.  Every call looks at that word
+ * first; if an earlier launch on this device left a code there, the call returns
+ * FA8_ERR_DEVICE_TIMEOUT (fa8_last_error_detail names the code), enqueues nothing but the
+ * clearing of the status words, and the call after it starts clean.  So a caller that never
+ * calls fa8_check_status still hears of a failed launch, at the latest from the first call made
+ * after that launch ended (the reference exits the process, include/attention_api.cuh:20-29).
+ * The first call on a device allocates that word (one cudaHostAlloc of four bytes). */
 int fa8_fwd(const fa8_fwd_params* params, void* cuda_stream);
 
 /* Reads a status word back after synchronising `cuda_stream`: FA8_OK,
  * FA8_ERR_DEVICE_TIMEOUT (code copied to *code_out if not NULL) or FA8_ERR_CUDA.
+ * status_word NULL = the library's own word of the current device, which is cleared once
+ * its code has been reported; a caller's word is left for the caller to clear.
  * Replaces the reference's cudaDeviceSynchronize + CUDA_ERROR_CHECK
  * (csrc/flash_attention.cu:663-665). */
 int fa8_check_status(const int32_t* status_word, void* cuda_stream, int32_t* code_out);
@@ -127,13 +144,15 @@ int fa8_quantize_e4m3_segments(const void* src, int32_t src_dtype, void* dst, in
  * exit(), include/attention_api.cuh:20-29): enqueues a one-warp kernel that waits on a barrier
  * nobody completes, using the same bounded wait as the attention kernel.  After `limit_us`
  * microseconds (1..1000000) the wait gives up, the kernel stores 0x7e57 in *status_word and
- * returns; fa8_check_status then reports FA8_ERR_DEVICE_TIMEOUT and the CUDA context stays
- * usable.  Nothing faults, traps or hangs. */
+ * returns; fa8_check_status then reports FA8_ERR_DEVICE_TIMEOUT (and so does the next fa8_fwd
+ * on the device, if that comes first) and the CUDA context stays usable.  status_word NULL =
+ * the library's own word.  Nothing faults, traps or hangs. */
 int fa8_selftest_expired_wait(int32_t* status_word, uint32_t limit_us, void* cuda_stream);
 
-/* Says whether fa8_fwd implements this shape: FA8_OK or FA8_ERR_UNSUPPORTED.  Replaces the
- * head_dim switch of the reference (csrc/static_switch.h:50-77). */
-int fa8_supported(int32_t seqlen, int32_t head_dim, int32_t v_layout);
+/* Says whether fa8_fwd implements this shape: FA8_OK or FA8_ERR_UNSUPPORTED.  `seqlen_k` is
+ * the key/value length (the query length is free).  Replaces the head_dim switch of the
+ * reference (csrc/static_switch.h:50-77). */
+int fa8_supported(int32_t seqlen_k, int32_t head_dim, int32_t v_layout);
 
 /* Static text for a return code.  Replaces the message printed by CUDA_ERROR_CHECK
  * (include/attention_api.cuh:20-29). */
@@ -144,7 +163,8 @@ const char* fa8_last_error_detail(void);
 
 /* ABI version of this header: major*100 + minor (101 added softmax_lse, 102 heads_kv, 103 the
  * descale pointers and fa8_quantize_e4m3, 104 fp8_format, 105 seqlen_k, 106 descale_per_head and
- * fa8_quantize_e4m3_segments; new fields go at
+ * fa8_quantize_e4m3_segments, 107 the library-owned status word and host-side failure flag,
+ * sequence lengths free of the multiple-of-16 rule except for transposed V; new fields go at
  * the end of fa8_fwd_params). */
 int fa8_version(void);
 

@@ -37,6 +37,7 @@ import numpy as np
 import torch
 
 E4M3_MAX = 448.0
+LOG2E = 1.4426950408889634
 
 
 def _build_decode_table() -> np.ndarray:
@@ -132,6 +133,14 @@ def e5m2_round(x: np.ndarray) -> np.ndarray:
     return (np.sign(x) * val).astype(np.float32)
 
 
+def e4m3_round(x: torch.Tensor) -> torch.Tensor:
+    """fp32 tensor -> nearest e4m3 VALUE (fp32), round-to-nearest-even, saturating to +-448:
+    what cvt.rn.satfinite.e4m3x2.f32 gives.  Uses torch's cast after the clamp (the cast alone
+    turns values beyond the range into NaN); same result as e4m3_decode(e4m3_encode(x)), which
+    tests/test_oracle_cpu.py checks, at a fraction of the time."""
+    return x.clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).to(torch.float32)
+
+
 def _as_f32(x8) -> torch.Tensor:
     """Accepts uint8 bit patterns (numpy / torch) or a float8_e4m3fn tensor."""
     if isinstance(x8, np.ndarray):
@@ -181,9 +190,30 @@ def attention_reference_fp16(q8, k8, v8, causal: bool, softmax_scale: float) -> 
     return torch.matmul(p, v)
 
 
+# Polynomials for 2^f on [-1/2, 1/2] (minimax in relative error: 7.5e-5 and 1.7e-3), the ones
+# the sm_100a kernel evaluates on the FMA pipe for part of the exponentials.
+EXP2_POLY = {3: (0.99992806, 0.69326097, 0.24261114, 0.055171654),
+             2: (1.0004431, 0.703448, 0.23842894)}
+EXP2_POLY_LO, EXP2_POLY_HI = -126.0, 9.0
+
+
+def exp2_poly(x: torch.Tensor, degree: int) -> torch.Tensor:
+    """2^x the way the kernel's FMA-pipe path computes it: x clamped to [-126, 9], split into
+    n = round-to-nearest(x) and f = x - n, polynomial in f, exponent added exactly."""
+    x = x.double().clamp(EXP2_POLY_LO, EXP2_POLY_HI)
+    n = torch.round(x)                       # ties to even, like the magic-number addition
+    f = (x - n).float().double()
+    c = EXP2_POLY[degree]
+    r = torch.full_like(f, c[-1])
+    for ck in reversed(c[:-1]):
+        r = (r * f + ck).float().double()    # one rounding per fused multiply-add
+    return (r * torch.exp2(n)).float()
+
+
 def attention_quantised_p(q8, k8, v8, causal: bool, softmax_scale: float, block_n: int = 128,
                           o_scale: float = 1.0, lazy: bool = False, lazy_limit: float = 256.0,
-                          lazy_rows: int = 32, p_format: str = "e4m3") -> torch.Tensor:
+                          lazy_rows: int = 32, p_format: str = "e4m3", poly_mask: int = 0,
+                          poly_degree: int = 3) -> torch.Tensor:
     """Model of an FP8 kernel (see module docstring).  Raw fp8 values are used
     as they are (no descale), like the reference kernel; P is rounded to `p_format`
     ("e4m3", or "e5m2" when the inputs are e5m2, csrc/flash_attention.cu:163-179,631).
@@ -195,7 +225,11 @@ def attention_quantised_p(q8, k8, v8, causal: bool, softmax_scale: float, block_
     kernel: after the first block m is kept until, within a group of `lazy_rows`
     consecutive query rows, some row's block sum of P exceeds `lazy_limit`; only then
     m, l and the accumulator of the whole group are brought up to date.  Both give the
-    same O/l up to the rounding of P."""
+    same O/l up to the rounding of P.
+
+    poly_mask: bit p set = the key columns 2p and 2p+1 of every block (block_n <= 64) take their
+    exponential from exp2_poly(., poly_degree) instead of exp, as the kernel does on the FMA
+    pipe; the row sum is taken from whatever P was computed, as in the kernel."""
     q = _as_f32(q8)
     k = _as_f32(k8)
     v = _as_f32(v8)
@@ -225,9 +259,15 @@ def attention_quantised_p(q8, k8, v8, causal: bool, softmax_scale: float, block_
                                     torch.exp((m - m_new) * softmax_scale))
                 m_eff = torch.where(torch.isinf(m_new), torch.zeros_like(m_new), m_new)
                 p = torch.exp(s * softmax_scale - (m_eff * softmax_scale).unsqueeze(1))
+                if poly_mask:
+                    c_log2 = softmax_scale * LOG2E
+                    cols_in = torch.arange(n1 - n0)
+                    sel = ((poly_mask >> (cols_in // 2)) & 1).bool()
+                    x2 = (s[:, sel] * c_log2 - (m_eff * c_log2).unsqueeze(1))
+                    p = p.clone()
+                    p[:, sel] = exp2_poly(x2, poly_degree)
                 l = l * alpha + p.sum(dim=1)
-                p8 = torch.from_numpy(e5m2_round(p.numpy()) if p_format == "e5m2"
-                                      else e4m3_decode(e4m3_encode(p.numpy())))
+                p8 = torch.from_numpy(e5m2_round(p.numpy())) if p_format == "e5m2" else e4m3_round(p)
                 acc = acc * alpha.unsqueeze(1) + p8 @ v[b, h, n0:n1]
                 m = m_new
             inv = torch.where((l == 0) | torch.isnan(l), torch.ones_like(l), 1.0 / l)

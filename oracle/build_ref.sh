@@ -19,9 +19,13 @@
 #   * the python module is named attention_cutlass_fp8_ref so that it can sit
 #     beside this repo's own attention_cutlass_fp8.
 #
-# Usage: oracle/build_ref.sh [REFERENCE_DIR]     (default /root/reference)
+# Usage: oracle/build_ref.sh REFERENCE_DIR     (or FA8_REFERENCE_DIR in the environment)
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${FA8_REFERENCE_DIR:-}}"
+if [ -z "$REF" ] || [ ! -d "$REF/csrc" ]; then
+  echo "usage: $0 REFERENCE_DIR (a checkout of weishengying/cutlass_flash_atten_fp8)" >&2
+  exit 2
+fi
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"
 PY="${PYTHON:-python}"

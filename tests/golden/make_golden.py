@@ -2,7 +2,7 @@
 oracle function, ``self_attention`` of the reference's test.py (lines 25-33), on
 CPU.  Run once in a container where the reference checkout is present:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 test.py imports two GPU-only extensions at module level and allocates its mask
 with device="cuda".  Neither is touched in the reference tree: the two imports
@@ -20,7 +20,9 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FA8_REFERENCE_DIR", "")
+if not os.path.isfile(os.path.join(REF, "test.py")):
+    sys.exit("usage: make_golden.py REFERENCE_DIR (a checkout of weishengying/cutlass_flash_atten_fp8)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

@@ -18,7 +18,7 @@ def test_library_builds_and_loads():
     build()
     assert os.path.exists(LIB_PATH)
     lib = _lib.load()
-    assert lib.fa8_version() == 106
+    assert lib.fa8_version() == 107
 
 
 def test_every_declared_symbol_is_exported():
@@ -41,7 +41,11 @@ def test_error_strings_and_support_query():
     assert lib.fa8_supported(128, 256, _lib.FA8_V_NATURAL) == _lib.FA8_OK
     assert lib.fa8_supported(128, 48, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
     assert lib.fa8_supported(128, 288, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
+    # only V^T has the sequence as its contiguous axis (row strides of 16 bytes for the copy engine)
     assert lib.fa8_supported(100, 64, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
+    assert lib.fa8_supported(100, 64, _lib.FA8_V_NATURAL) == _lib.FA8_OK
+    assert lib.fa8_supported(1, 128, _lib.FA8_V_NATURAL) == _lib.FA8_OK
+    assert b"multiple of 32" in lib.fa8_error_string(_lib.FA8_ERR_UNSUPPORTED)
     assert lib.fa8_supported(0, 64, _lib.FA8_V_TRANSPOSED) == _lib.FA8_ERR_UNSUPPORTED
 
 
@@ -63,4 +67,22 @@ def test_argument_validation_needs_no_gpu():
     p.head_dim = 64
     p.v_layout = 7
     assert lib.fa8_fwd(ctypes.byref(p), None) == _lib.FA8_ERR_BAD_ARG
+    # without a device there is no library-owned status word to fall back on
     assert lib.fa8_check_status(None, None, None) == _lib.FA8_ERR_BAD_ARG
+    assert lib.fa8_selftest_expired_wait(None, 1000, None) == _lib.FA8_ERR_BAD_ARG
+
+
+def test_stale_library_is_not_loaded_silently(tmp_path, monkeypatch):
+    from cutlass_flash_atten_fp8_b200 import build as b
+    build()
+    assert not b.is_stale()
+    monkeypatch.setattr(b, "source_digest", lambda: "0" * 64)
+    assert b.is_stale()
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "is_stale", b.is_stale)
+    try:
+        _lib.load()
+    except ImportError as e:
+        assert "older than its sources" in str(e)
+    else:
+        raise AssertionError("a stale library was loaded")

@@ -16,8 +16,37 @@ def test_operator_rejects_host_tensors_like_the_reference():
 
 
 def test_drop_in_module_name():
+    # the reference's module name (setup.py:45, test.py:3): the compiled torch binding when it
+    # has been built (an extension module is found ahead of a .py of the same name), else the
+    # ctypes operator re-exported by attention_cutlass_fp8.py
     import attention_cutlass_fp8
-    assert attention_cutlass_fp8.flash_attention_v2_cutlass is flash_attention_v2_cutlass
+    fn = attention_cutlass_fp8.flash_attention_v2_cutlass
+    if attention_cutlass_fp8.__file__.endswith(".py"):
+        assert fn is flash_attention_v2_cutlass
+    else:
+        assert "is_causal: bool = False" in fn.__doc__ and "softmax_scale" in fn.__doc__
+
+
+def test_compiled_binding_builds_and_checks_its_inputs_like_the_reference():
+    import importlib.util
+
+    from cutlass_flash_atten_fp8_b200 import _lib
+    from cutlass_flash_atten_fp8_b200.build import build_binding
+    path = build_binding()
+    spec = importlib.util.spec_from_file_location("attention_cutlass_fp8", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.abi_version() == _lib.load().fa8_version()
+    q = torch.zeros(1, 1, 128, 64).to(F8)
+    with pytest.raises(RuntimeError, match="q must be a CUDA tensor"):      # CHECK_CUDA, include/attention_api.cuh:12-13
+        mod.flash_attention_v2_cutlass(q, q, q.transpose(2, 3).contiguous(), False, 0.125)
+
+
+def test_quantize_per_head_wants_three_dimensions_before_anything_else():
+    from cutlass_flash_atten_fp8_b200 import api
+    x = torch.zeros(8, dtype=torch.float16)
+    with pytest.raises(RuntimeError):          # a host tensor: CHECK_INPUT fires first, never an IndexError
+        api.quantize_e4m3(x, per_head=True)
 
 
 @pytest.mark.parametrize("n,world", [(2048, 8), (512, 4), (7, 3), (3, 8), (0, 2), (64, 1)])

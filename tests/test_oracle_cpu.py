@@ -128,3 +128,31 @@ def test_descales_fold_into_scale_and_output():
     a = attention_fp32(q, k, v, False, 0.125, dq, dk, dv)
     b = attention_fp32(q, k, v, False, 0.125 * dq * dk) * dv
     assert torch.allclose(a, b, rtol=1e-4, atol=1e-6)
+
+
+def test_fast_e4m3_rounding_equals_the_bit_level_one():
+    from oracle.attention_oracle import e4m3_decode, e4m3_encode, e4m3_round
+    g = torch.Generator().manual_seed(21)
+    x = torch.cat([torch.randn(200000, generator=g) * s for s in (1e-3, 0.05, 1.0, 30.0, 400.0)])
+    x = torch.cat([x, torch.tensor([0.0, 448.0, 449.0, 464.0, 480.0, 1e6, 2.0 ** -9, 2.0 ** -10, 1.5 * 2.0 ** -10,
+                                    2.0 ** -10 * 0.999, 0.0078125 + 0.0009765625])])
+    want = torch.from_numpy(e4m3_decode(e4m3_encode(x.numpy())))
+    assert torch.equal(e4m3_round(x), want)
+
+
+def test_polynomial_exponential_model():
+    from oracle.attention_oracle import exp2_poly
+    x = torch.linspace(-140.0, 12.0, 50001)
+    t = torch.exp2(x.double().clamp(-126.0, 9.0))
+    for deg, tol in ((3, 8e-5), (2, 1.8e-3)):
+        r = exp2_poly(x, deg).double()
+        assert float(((r - t) / t).abs().max()) <= tol
+    # on part of the columns it moves the model by far less than its distance to the fp32 oracle
+    q, k, v = _rand8(1, 1, 512, 128, seed=30), _rand8(1, 1, 512, 128, seed=31), _rand8(1, 1, 512, 128, seed=32)
+    sc = 1 / math.sqrt(128)
+    a = attention_quantised_p(q, k, v, True, sc, block_n=64, lazy=True, lazy_limit=448.0)
+    b = attention_quantised_p(q, k, v, True, sc, block_n=64, lazy=True, lazy_limit=448.0, poly_mask=0x11111111,
+                              poly_degree=2)
+    ref = attention_fp32(q, k, v, True, sc)
+    assert error_metrics(a, b)["rel_l2"] < 1e-2
+    assert abs(error_metrics(a, ref)["rel_l2"] - error_metrics(b, ref)["rel_l2"]) < 2e-3

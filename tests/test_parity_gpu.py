@@ -102,6 +102,32 @@ def test_ragged_sequence_lengths(S):
         assert_close_to_oracles(out, q8, k8, v8, causal, 1 / math.sqrt(D))
 
 
+@pytest.mark.parametrize("Sq,Sk", [(100, 100), (77, 333), (1, 64), (130, 17), (257, 1000)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_any_sequence_length_with_natural_v(Sq, Sk, causal):
+    """Only V^T has the sequence as its contiguous axis (rows of seqlen_k bytes, which the copy
+    engine wants in multiples of 16): with V in its natural layout every length is accepted."""
+    d = dev()
+    for D in (64, 128):
+        q8 = rand8(2, 2, Sq, D, seed=Sq + D)
+        k8, v8 = rand8(2, 2, Sk, D, seed=Sk + D + 1), rand8(2, 2, Sk, D, seed=Sk + D + 2)
+        scale = 1 / math.sqrt(D)
+        guard = torch.full((2 * 2 * Sq * D + 64,), float("nan"), dtype=torch.float16, device=d)
+        out = flash_attention_v2_cutlass(q8.to(d), k8.to(d), v8.to(d), causal, scale, v_layout="natural",
+                                         out=guard[:2 * 2 * Sq * D].view(2, 2, Sq, D))[0]
+        check_status(d)
+        assert bool(torch.isnan(guard[2 * 2 * Sq * D:]).all())
+        s = torch.matmul(q8.float(), k8.float().transpose(2, 3)) * scale
+        if causal:
+            s = s.masked_fill(torch.arange(Sk).unsqueeze(0) > torch.arange(Sq).unsqueeze(1), float("-inf"))
+        ref = torch.softmax(s, dim=-1) @ v8.float()
+        m = error_metrics(out, ref)
+        assert m["rel_l2"] <= REL_L2_FP32 and m["max_abs"] <= MAX_ABS_FRAC_FP32 * m["max_ref"], (D, m)
+    with pytest.raises(RuntimeError, match="unsupported"):     # transposed V still needs a multiple of 16
+        x = torch.zeros(1, 1, 100, 64, device=d).to(F8)
+        flash_attention_v2_cutlass(x, x, x.transpose(2, 3).contiguous(), False, 0.125)
+
+
 def test_tiny_config_with_per_tensor_scales():
     # B1 H2 S128 D64 non-causal, N(0,1) amax-scaled to e4m3; descales folded by the caller
     w = synth.WORKLOADS["tiny"]
@@ -283,11 +309,27 @@ def _sampled_rows_check(q8, k8, vt8, out, slices, causal, scale, dv=1.0, n_rows=
         assert m["max_abs"] <= MAX_ABS_FRAC_FP32 * m["max_ref"], (s, m)
 
 
+def _whole_slice_check(q8, k8, vt8, out, s, causal, scale, dv):
+    """Every row of slice `s` against the fp32 oracle and against the kernel model (the tight
+    one: it is what would catch a wrong rescale when the lazily raised maximum fires)."""
+    S, D = q8.shape[1], q8.shape[2]
+    q, k = q8[s].cpu().view(1, 1, S, D), k8[s].cpu().view(1, 1, S, D)
+    v = vt8[s].t().contiguous().cpu().view(1, 1, S, D)
+    o = out[s].float().cpu().view(1, 1, S, D)
+    m = error_metrics(o, attention_fp32(q, k, v, causal, scale) * dv)
+    assert m["rel_l2"] <= REL_L2_FP32 and m["max_abs"] <= MAX_ABS_FRAC_FP32 * m["max_ref"], (s, m)
+    model = attention_quantised_p(q, k, v, causal, scale, o_scale=dv, **KERNEL_MODEL)
+    mm = error_metrics(o, model)
+    assert mm["rel_l2"] <= REL_L2_MODEL, (s, mm)
+
+
 @pytest.mark.parametrize("name", ["prefill_s1024_d64", "mid_s4096_d128", "mid_s4096_d128_causal",
                                   "long_s16384_d128_causal"])
 def test_full_size_configs(name):
-    """Full-size BASELINE configs: sampled rows against the fp32 oracle, shard invariance
-    (a sub-range of slices computed alone is bitwise the same), determinism."""
+    """Full-size BASELINE configs on their own synthetic data (per-tensor scales, the +-8 sigma
+    outliers of the mid-length config included): one whole slice, all rows, against the fp32
+    oracle and the kernel model; sampled rows of three more slices against the fp32 oracle;
+    shard invariance (a sub-range of slices computed alone is bitwise the same)."""
     w = synth.WORKLOADS[name]
     d = dev()
     q8, k8, vt8, (dq, dk, dv) = synth.make_qkv(w, d)
@@ -297,6 +339,7 @@ def test_full_size_configs(name):
     out = flash_attention_v2_cutlass(as4(q8), as4(k8), as4(vt8), w.causal, scale, o_scale=dv)[0][0]
     check_status(d)
     assert not torch.isnan(out).any()
+    _whole_slice_check(q8, k8, vt8, out, n // 3, w.causal, scale, dv)
     _sampled_rows_check(q8, k8, vt8, out, [0, n // 2, n - 1], w.causal, scale, dv)
     lo, hi = n // 4, n // 4 + max(1, n // 8)
     part = flash_attention_v2_cutlass(as4(q8[lo:hi]), as4(k8[lo:hi]), as4(vt8[lo:hi]), w.causal, scale, o_scale=dv)[0][0]
@@ -305,22 +348,25 @@ def test_full_size_configs(name):
 
 
 def test_box_scale_config_shape():
-    """B64 H32 S8192 D128 causal (2048 slices, the largest grid.y and >2^31-byte tensors):
-    iid N(0,1) inputs, sampled rows of the first, a middle and the last slice."""
+    """B64 H32 S8192 D128 causal (2048 slices, the largest grid and tensors beyond 2^31 bytes) on
+    the workload's own data - iid N(0,1), per-tensor amax scaling, descales folded the way the
+    benchmark folds them: one whole slice against both oracles, sampled rows of the first, a
+    middle and the last slice, and a shard of 256 slices (one rank of eight) bitwise equal."""
     w = synth.WORKLOADS["box_s8192_d128_causal"]
     d = dev()
     n, S, D = w.n_slices, w.seqlen, w.head_dim
-    g = torch.Generator(device=d).manual_seed(w.seed)
-    def draw(shape):
-        t = torch.empty(shape, dtype=F8, device=d)
-        for i in range(0, n, 128):
-            t[i:i + 128] = (torch.randn((128,) + shape[1:], generator=g, device=d) * 100.0).clamp(-448.0, 448.0).to(F8)
-        return t
-    q8, k8, vt8 = draw((n, S, D)), draw((n, S, D)), draw((n, D, S))
-    scale = w.softmax_scale / 100.0 / 100.0
-    out = flash_attention_v2_cutlass(q8.view(1, n, S, D), k8.view(1, n, S, D), vt8.view(1, n, D, S), True, scale)[0][0]
+    q8, k8, vt8, (dq, dk, dv) = synth.make_qkv(w, d)
+    scale = w.softmax_scale * dq * dk
+    out = flash_attention_v2_cutlass(q8.view(1, n, S, D), k8.view(1, n, S, D), vt8.view(1, n, D, S), True, scale,
+                                     o_scale=dv)[0][0]
     check_status(d)
-    _sampled_rows_check(q8, k8, vt8, out, [0, 1023, n - 1], True, scale, n_rows=128)
+    _whole_slice_check(q8, k8, vt8, out, 777, True, scale, dv)
+    _sampled_rows_check(q8, k8, vt8, out, [0, 1023, n - 1], True, scale, dv, n_rows=128)
+    lo, hi = 3 * 256, 4 * 256
+    part = flash_attention_v2_cutlass(q8[lo:hi].view(1, 256, S, D), k8[lo:hi].view(1, 256, S, D),
+                                      vt8[lo:hi].view(1, 256, D, S), True, scale, o_scale=dv)[0][0]
+    check_status(d)
+    assert torch.equal(part, out[lo:hi])
 
 
 @pytest.mark.parametrize("Hk,layout,lse", [(6, "transposed", False), (6, "natural", True), (2, "natural", False)])

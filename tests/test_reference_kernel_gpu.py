@@ -68,3 +68,50 @@ def test_against_reference_kernel(D, causal):
     assert float(within) >= 0.99, float(within)
     # this library's unrounded output is at least as close to the naive result
     assert float((ours_f - naive).abs().mean()) <= float((theirs_f - naive).abs().mean()) * 1.05
+
+
+@pytest.mark.parametrize("name,n_slices", [("prefill_s1024_d64", 8), ("mid_s4096_d128", 4), ("mid_s4096_d128_causal", 4),
+                                           ("long_s16384_d128_causal", 2)])
+def test_baseline_configs_against_reference_kernel(name, n_slices):
+    """The shapes of the benchmark configurations on their own synthetic data (N(0,1) values,
+    per-tensor amax scaling, the +-8 sigma outliers of the mid-length one), a few (batch, head)
+    slices each: the raw e4m3 values go to both kernels with the descales folded into the softmax
+    scale; this library's fp16 O is rounded to e4m3 for the element-wise comparison (the reference
+    stores e4m3, csrc/flash_attention.cu:556-557).  Both are compared with the fp32 oracle: this
+    library's unrounded O must not be further from it than the reference's."""
+    from cutlass_flash_atten_fp8_b200 import synth
+    from oracle.attention_oracle import attention_fp32, error_metrics
+    ref = _load_reference()
+    dev = torch.device("cuda", 0)
+    w = synth.WORKLOADS[name]
+    q8, k8, vt8, (dq, dk, dv) = synth.make_qkv(w, dev, 0, n_slices)
+    S, D = w.seqlen, w.head_dim
+    q, k, vt = q8.view(1, n_slices, S, D), k8.view(1, n_slices, S, D), vt8.view(1, n_slices, D, S)
+    scale = w.softmax_scale * dq * dk
+    theirs = ref.flash_attention_v2_cutlass(q, k, vt, w.causal, scale)[0]
+    ours = flash_attention_v2_cutlass(q, k, vt, w.causal, scale)[0]
+    check_status(dev)
+    theirs_f, ours_f = theirs.float().cpu(), ours.float().cpu()
+    ours_q = ours.float().clamp(-448.0, 448.0).to(F8).float().cpu()
+    oracle = attention_fp32(q8.cpu().view(1, n_slices, S, D), k8.cpu().view(1, n_slices, S, D),
+                            vt8.transpose(1, 2).contiguous().cpu().view(1, n_slices, S, D), w.causal, scale)
+    e_ours, e_theirs = error_metrics(ours_f, oracle), error_metrics(theirs_f, oracle)
+    e_ours_q = error_metrics(ours_q, oracle)
+    # Element by element the two agree to one e4m3 step of the reference's value, or - for the
+    # elements that are small beside the output's typical size, where the rounding of P that both
+    # kernels do (at different tile sizes) moves a value by more than its own e4m3 step - to
+    # three times the noise either kernel shows against the fp32 oracle.
+    rms = float(oracle.pow(2).mean().sqrt())
+    noise = max(e_ours["rel_l2"], e_theirs["rel_l2"]) * rms
+    tol = torch.maximum(_e4m3_step(theirs_f) * 1.001, torch.full_like(theirs_f, 3.0 * noise))
+    within = float(((ours_q - theirs_f).abs() <= tol).float().mean())
+    one_step = float(((ours_q - theirs_f).abs() <= _e4m3_step(theirs_f) * 1.001).float().mean())
+    between = error_metrics(ours_q, theirs_f)["rel_l2"]
+    print(f"{name}: within tolerance {within:.4f} (one e4m3 step alone {one_step:.4f}); rel-L2 vs fp32: ours "
+          f"{e_ours['rel_l2']:.4f}, ours rounded to e4m3 {e_ours_q['rel_l2']:.4f}, reference {e_theirs['rel_l2']:.4f}; "
+          f"ours rounded vs reference {between:.4f}")
+    assert within >= 0.99, within
+    # both sit near the oracle, so they sit near each other
+    assert between <= e_ours_q["rel_l2"] + e_theirs["rel_l2"], (between, e_ours_q, e_theirs)
+    # this library's unrounded output is at least as close to the oracle as the reference's
+    assert e_ours["rel_l2"] <= e_theirs["rel_l2"] * 1.02, (e_ours, e_theirs)
