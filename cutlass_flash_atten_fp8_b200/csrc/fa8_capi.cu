@@ -68,6 +68,29 @@ bool make_map_3d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t mi
   return true;
 }
 
+// O: 3-D fp16 tensor {head_dim, seqlen, slices}, stored through {box_cols, 32, 1} boxes, no swizzle.
+bool make_map_o(CUtensorMap* out, void* base, uint64_t head_dim, uint64_t seqlen, uint64_t slices, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) {
+    set_detail("cudaGetDriverEntryPoint", "cuTensorMapEncodeTiled not available");
+    return false;
+  }
+  cuuint64_t dims[3] = {head_dim, seqlen, slices};
+  cuuint64_t strides[2] = {head_dim * 2, head_dim * seqlen * 2};   // bytes, for dims 1 and 2
+  cuuint32_t box[3] = {box_cols, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
+    set_detail("cuTensorMapEncodeTiled (O)", buf);
+    return false;
+  }
+  return true;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // The library's own status word, one per device that loads the module: used when the caller
@@ -203,7 +226,9 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   const uint32_t d_box = (p->head_dim <= 64) ? 64u : (p->head_dim <= 128 ? 128u : 256u);
   const uint32_t d_blk = d_box < 128u ? d_box : 128u;
   const CUtensorMapSwizzle sw_qk = (d_box >= 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
+  if (!make_map_o(&to, p->o, D, S, static_cast<uint64_t>(bh), static_cast<uint32_t>(fa8::epi_cols(static_cast<int>(d_box)))))
+    return FA8_ERR_CUDA;
   if (!make_map_3d(&tq, p->q, D, S, bh, d_blk, 128, sw_qk)) return FA8_ERR_CUDA;
   if (!make_map_3d(&tk, p->k, D, Sk, bh_kv, d_blk, 128, sw_qk)) return FA8_ERR_CUDA;
   if (p->v_layout == FA8_V_NATURAL) {
@@ -239,7 +264,7 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   if (bh * per_slice > 0x7fffffff) return FA8_ERR_UNSUPPORTED;
   args.n_units = static_cast<int>(bh * per_slice);
   cudaError_t e = fa8::launch_fwd(static_cast<int>(d_box), p->is_causal != 0, p->v_layout == FA8_V_NATURAL,
-                                  p->fp8_format == FA8_FP8_E5M2, tq, tk, tv, args, stream);
+                                  p->fp8_format == FA8_FP8_E5M2, tq, tk, tv, to, args, stream);
   if (e != cudaSuccess) {
     set_detail("kernel launch", cudaGetErrorString(e));
     return FA8_ERR_CUDA;

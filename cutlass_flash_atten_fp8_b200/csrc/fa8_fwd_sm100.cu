@@ -129,7 +129,16 @@ struct Cfg {
   static constexpr int kSlots = (D == 128) ? 8 : (D == 64 ? 16 : 4);   // ring slots, one K or V tile each
   static constexpr int kQBytes = 2 * kTiles * kTileBytes;  // tiles x two stages (work items)
   static constexpr int kRingBytes = kSlots * kTileBytes;
-  static constexpr int kBarOffset = kQBytes + kRingBytes;
+  // Write-out of O: every softmax warp stages 32 rows x kEpiCols fp16 columns in shared memory
+  // and hands them to the copy engine as one tiled store (a thread storing its own row straight
+  // from registers touches 32 different 128-byte lines per instruction; measured, that made the
+  // write-out of a work item cost 2600 cycles).  The width is what the shared memory left beside
+  // the ring allows: 2 KB per warp, 1 KB at head_dim 128.
+  static constexpr int kEpiCols = (D == 128) ? 16 : 32;
+  static constexpr int kEpiBytes = 32 * kEpiCols * 2;                  // per warp
+  static constexpr int kEpiWarps = 4 * kW * kTiles;                    // softmax warps that have rows
+  static constexpr int kEpiOffset = kQBytes + kRingBytes;
+  static constexpr int kBarOffset = kEpiOffset + kEpiWarps * kEpiBytes;
   // row-group scratch shared by the warps of a 32-row group, see RowGroupShared
   static constexpr int kGroups = 16 / kW;          // one per 32-row group of a tile slot (slot 1 idles at head_dim 256)
   static constexpr int kGroupBytes = kGroups * (160 + 512 * kW);
@@ -445,7 +454,8 @@ __device__ __forceinline__ bool get_item(const KernelArgs& a, int unit, int k, I
 template <int D, bool kCausal, bool kVNatural, bool kE5M2>
 __global__ void __launch_bounds__(kThreads, 1)
 fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const KernelArgs args) {
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+               const KernelArgs args) {
   using C = Cfg<D>;
   constexpr int kItemsPerUnit = kCausal ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
@@ -845,6 +855,9 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       float c = args.scale_log2 * qk_descale;
       float sm_scale = args.softmax_scale * qk_descale;
       RowGroupShared<kW>& grp = groups[i * 4 + quarter];
+      // This warp's staging buffer for the write-out of O (warps without rows have none).
+      const uint32_t s_stage = smem_base + C::kEpiOffset + static_cast<uint32_t>(warp % C::kEpiWarps) * C::kEpiBytes;
+      if (lane == 0) prefetch_tensormap(&tm_o);
       // Running phases of the barriers this warp waits on.  Sub-block sb of an item uses phase
       // number (uses of its buffer in earlier items) + sb / kNB of s_full and p_full alike; bit b
       // of ph_bits is the parity of the first of these for buffer b.
@@ -1002,34 +1015,47 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           const float inv = ((l_tot == 0.f || l_tot != l_tot) ? 1.f : 1.f / l_tot) * o_scale;
           if (args.lse != nullptr && h == 0 && q_row < seqlen)    // log(sum exp(scale*s)) = scale*m + log(l)
             args.lse[static_cast<size_t>(w.bh) * seqlen + q_row] = m_fin * sm_scale + __logf(l_tot);
-          // Rows of O are args.head_dim long; the kernel's columns beyond that are padding.
+          // Rows of O are args.head_dim long; the kernel's columns beyond that are padding, and
+          // the tile may reach past the last query row: the copy engine drops both.
           const int d_out = args.head_dim;
           constexpr int kMyCols = D / kW;                     // this warp's share of the head dimension
-          __half* o_row = args.o + (static_cast<size_t>(w.bh) * seqlen + q_row) * d_out + h * kMyCols;
+          constexpr int kEC = C::kEpiCols;
+          const int row0_warp = w.row0 + i * kTileM + quarter * 32;
   #pragma unroll
-          for (int q = 0; q < kMyCols / 32; ++q) {
-            uint32_t orow[32];
-            tmem_ld_32x32b_x32(t_o + h * kMyCols + 32 * q, orow);
+          for (int q = 0; q < kMyCols / kEC; ++q) {
+            uint32_t orow[kEC];
+            if constexpr (kEC == 16) tmem_ld_32x32b_x16(t_o + h * kMyCols + kEC * q, orow);
+            else tmem_ld_32x32b_x32(t_o + h * kMyCols + kEC * q, orow);
+            // the staging buffer is free once the copy engine has read the store before this one
+            if (lane == 0) bulk_wait_group_read0();
             tmem_wait_ld();
-            if (q == kMyCols / 32 - 1) {
+            if (q == kMyCols / kEC - 1) {
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive(bar_o_free(i));      // the next item's PV may overwrite O_i
+            } else {
+              __syncwarp();
             }
-            if (q_row < seqlen && h * kMyCols + 32 * q < d_out) {       // head_dim is a multiple of 32
   #pragma unroll
-              for (int e = 0; e < 32; e += 8) {
-                st_global_v4(o_row + 32 * q + e,
-                             pack_half2(__uint_as_float(orow[e + 0]) * inv, __uint_as_float(orow[e + 1]) * inv),
-                             pack_half2(__uint_as_float(orow[e + 2]) * inv, __uint_as_float(orow[e + 3]) * inv),
-                             pack_half2(__uint_as_float(orow[e + 4]) * inv, __uint_as_float(orow[e + 5]) * inv),
-                             pack_half2(__uint_as_float(orow[e + 6]) * inv, __uint_as_float(orow[e + 7]) * inv));
-              }
+            for (int e = 0; e < kEC; e += 8) {
+              st_shared_v4(s_stage + static_cast<uint32_t>(lane * kEC * 2 + e * 2),
+                           pack_half2(__uint_as_float(orow[e + 0]) * inv, __uint_as_float(orow[e + 1]) * inv),
+                           pack_half2(__uint_as_float(orow[e + 2]) * inv, __uint_as_float(orow[e + 3]) * inv),
+                           pack_half2(__uint_as_float(orow[e + 4]) * inv, __uint_as_float(orow[e + 5]) * inv),
+                           pack_half2(__uint_as_float(orow[e + 6]) * inv, __uint_as_float(orow[e + 7]) * inv));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            const int col0 = h * kMyCols + kEC * q;
+            if (lane == 0 && col0 < d_out && row0_warp < seqlen) {
+              tma_store_3d(&tm_o, s_stage, col0, row0_warp, w.bh);
+              bulk_commit_group();
             }
           }
           ++items;
         }
       }
+      if (lane == 0) bulk_wait_group0();      // this warp's stores of O have left shared memory and are complete
     }
   }
 
@@ -1069,7 +1095,7 @@ static constexpr int smem_bytes_for() { return Cfg<D>::kSmemBytes; }
 
 template <int D, bool kCausal, bool kVNatural, bool kE5M2>
 static cudaError_t launch_one(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                              const KernelArgs& args, cudaStream_t stream) {
+                              const CUtensorMap& to, const KernelArgs& args, cudaStream_t stream) {
   auto kernel = &fa8_fwd_kernel<D, kCausal, kVNatural, kE5M2>;
   constexpr int smem = Cfg<D>::kSmemBytes;
   // Per device and kernel variant: the shared-memory opt-in is made once, and the SM count is
@@ -1098,41 +1124,42 @@ static cudaError_t launch_one(const CUtensorMap& tq, const CUtensorMap& tk, cons
 #else
   dim3 grid(args.n_units < sms ? args.n_units : sms, 1, 1);
 #endif
-  kernel<<<grid, kThreads, smem, stream>>>(tq, tk, tv, args);
+  kernel<<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, args);
   return cudaGetLastError();
 }
 
 template <int D, bool kCausal>
 static cudaError_t launch_layout(bool v_natural, bool e5m2, const CUtensorMap& tq, const CUtensorMap& tk,
-                                 const CUtensorMap& tv, const KernelArgs& args, cudaStream_t stream) {
+                                 const CUtensorMap& tv, const CUtensorMap& to, const KernelArgs& args,
+                                 cudaStream_t stream) {
 #ifdef FA8_SUBSET
   if (v_natural || e5m2) return cudaErrorInvalidValue;
-  return launch_one<D, kCausal, false, false>(tq, tk, tv, args, stream);
+  return launch_one<D, kCausal, false, false>(tq, tk, tv, to, args, stream);
 #else
   if (v_natural) {
-    return e5m2 ? launch_one<D, kCausal, true, true>(tq, tk, tv, args, stream)
-                : launch_one<D, kCausal, true, false>(tq, tk, tv, args, stream);
+    return e5m2 ? launch_one<D, kCausal, true, true>(tq, tk, tv, to, args, stream)
+                : launch_one<D, kCausal, true, false>(tq, tk, tv, to, args, stream);
   }
-  return e5m2 ? launch_one<D, kCausal, false, true>(tq, tk, tv, args, stream)
-              : launch_one<D, kCausal, false, false>(tq, tk, tv, args, stream);
+  return e5m2 ? launch_one<D, kCausal, false, true>(tq, tk, tv, to, args, stream)
+              : launch_one<D, kCausal, false, false>(tq, tk, tv, to, args, stream);
 #endif
 }
 
 cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, const CUtensorMap& tq,
-                       const CUtensorMap& tk, const CUtensorMap& tv, const KernelArgs& args,
+                       const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to, const KernelArgs& args,
                        cudaStream_t stream) {
   if (head_dim == 128) {
-    return causal ? launch_layout<128, true>(v_natural, e5m2, tq, tk, tv, args, stream)
-                  : launch_layout<128, false>(v_natural, e5m2, tq, tk, tv, args, stream);
+    return causal ? launch_layout<128, true>(v_natural, e5m2, tq, tk, tv, to, args, stream)
+                  : launch_layout<128, false>(v_natural, e5m2, tq, tk, tv, to, args, stream);
   }
   if (head_dim == 64) {
-    return causal ? launch_layout<64, true>(v_natural, e5m2, tq, tk, tv, args, stream)
-                  : launch_layout<64, false>(v_natural, e5m2, tq, tk, tv, args, stream);
+    return causal ? launch_layout<64, true>(v_natural, e5m2, tq, tk, tv, to, args, stream)
+                  : launch_layout<64, false>(v_natural, e5m2, tq, tk, tv, to, args, stream);
   }
 #ifndef FA8_SUBSET
   if (head_dim == 256) {
-    return causal ? launch_layout<256, true>(v_natural, e5m2, tq, tk, tv, args, stream)
-                  : launch_layout<256, false>(v_natural, e5m2, tq, tk, tv, args, stream);
+    return causal ? launch_layout<256, true>(v_natural, e5m2, tq, tk, tv, to, args, stream)
+                  : launch_layout<256, false>(v_natural, e5m2, tq, tk, tv, to, args, stream);
   }
 #endif
   return cudaErrorInvalidValue;

@@ -40,9 +40,14 @@ struct KernelArgs {
 // v_natural: V is [slices, seqlen, head_dim] (tv describes it like K) instead of the
 // reference's transposed [slices, head_dim, seqlen].
 // e5m2: Q, K, V (and P) are e5m2 instead of e4m3.
+// to: O as a 3-D fp16 tensor {head_dim, seqlen, slices} with a {epi_cols(head_dim), 32, 1} box
+// (see epi_cols below), through which the softmax warps store their rows.
 cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, const CUtensorMap& tq,
-                       const CUtensorMap& tk, const CUtensorMap& tv, const KernelArgs& args,
+                       const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to, const KernelArgs& args,
                        cudaStream_t stream);
+
+// fp16 columns per store box of the kernel built for head dim 64, 128 or 256.
+constexpr int epi_cols(int kernel_head_dim) { return kernel_head_dim == 128 ? 16 : 32; }
 
 // One warp waits (bounded by limit_ns) on a barrier that never completes; see fa8_selftest_expired_wait.
 cudaError_t launch_expired_wait(int* status, int* host_status, unsigned long long limit_ns, cudaStream_t stream);
