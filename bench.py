@@ -43,14 +43,15 @@ DEFAULT_WORKLOAD = "mid_s4096_d128"
 # batch-2 cut of the same shape (64 slices instead of 512) was captured and the figure of the
 # full workload is that capture times 8: traffic is proportional to the number of slices.
 NCU_TRAFFIC_BYTES = {
-    # captured on mid_s4096_d128_b2 (64 slices): 100.74 MB read + 30.30 MB written (part of the
+    # captured on mid_s4096_d128_b2 (64 slices): 100.74 MB read + 36.30 MB written (part of the
     # fp16 output is still dirty in L2 at kernel end); traffic is proportional to the slice count,
     # the bench workload has 8x the slices
-    "mid_s4096_d128_b2": 131.0e6,
-    "mid_s4096_d128": 8 * 131.0e6,
-    "mid_s4096_d128_b2_causal": 128.6e6,
-    "mid_s4096_d128_causal": 8 * 128.6e6,
-    "prefill_s1024_d64": 129.9e6,
+    "mid_s4096_d128_b2": 137.0e6,
+    "mid_s4096_d128": 8 * 137.0e6,
+    "mid_s4096_d128_b2_causal": 134.9e6,
+    "mid_s4096_d128_causal": 8 * 134.9e6,
+    "prefill_s1024_d64": 134.8e6,
+    "mid_s4096_d256_b2": 137.8e6,
 }
 
 
