@@ -26,7 +26,8 @@ FA8_DTYPE_BF16 = 1
 # Every symbol include/fa8_b200.h declares.
 EXPORTED_SYMBOLS = ("fa8_fwd", "fa8_check_status", "fa8_supported", "fa8_error_string",
                     "fa8_last_error_detail", "fa8_version", "fa8_selftest_expired_wait",
-                    "fa8_quantize_e4m3", "fa8_quantize_e4m3_segments")
+                    "fa8_quantize_e4m3", "fa8_quantize_e4m3_segments", "fa8_quantize_e4m3_segments_noalloc")
+FA8_NOALLOC_MAX_SEGMENTS = 4096
 
 
 class Fa8FwdParams(ctypes.Structure):
@@ -71,6 +72,9 @@ def load() -> ctypes.CDLL:
     lib.fa8_quantize_e4m3_segments.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64,
                                                ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     lib.fa8_quantize_e4m3_segments.restype = ctypes.c_int
+    lib.fa8_quantize_e4m3_segments_noalloc.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64,
+                                                       ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+    lib.fa8_quantize_e4m3_segments_noalloc.restype = ctypes.c_int
     lib.fa8_supported.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.fa8_supported.restype = ctypes.c_int
     lib.fa8_error_string.argtypes = [ctypes.c_int]

@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -140,6 +141,33 @@ DeviceState* device_state() {
   return &st;
 }
 
+// Scratch of fa8_quantize_e4m3_segments_noalloc: the per-segment |x| maxima that the first pass
+// accumulates and the second pass reads.  A file-scope device array instead of memory from the
+// allocator: 16 KB on every GPU that loads the library, held until the process exits, shared by
+// every call (so it keeps the last call's contents and is cleared at the start of each).
+static __device__ __align__(256) float g_quant_amax_scratch[FA8_NOALLOC_MAX_SEGMENTS];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel can
+// use: the device address is asked for once per device, with that device current, and kept.
+std::atomic<float*> g_quant_scratch_addr[kMaxDevices];
+
+float* quant_scratch(cudaError_t* err) {
+  *err = cudaSuccess;
+  int dev = -1;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return nullptr;
+  const bool cached = dev >= 0 && dev < kMaxDevices;
+  if (cached) {
+    float* known = g_quant_scratch_addr[dev].load(std::memory_order_acquire);
+    if (known) return known;
+  }
+  void* addr = nullptr;
+  *err = cudaGetSymbolAddress(&addr, g_quant_amax_scratch);
+  if (*err != cudaSuccess) return nullptr;
+  if (cached) g_quant_scratch_addr[dev].store(static_cast<float*>(addr), std::memory_order_release);
+  return static_cast<float*>(addr);
+}
+
 // Collects a failure an earlier launch on this device left in the host flag: clears the flag
 // and, stream-ordered, the device words, and returns the code (0 = none).
 int collect_earlier_failure(DeviceState* st, int32_t* caller_word, cudaStream_t stream) {
@@ -156,7 +184,7 @@ int collect_earlier_failure(DeviceState* st, int32_t* caller_word, cudaStream_t 
 
 extern "C" {
 
-int fa8_version(void) { return 107; }
+int fa8_version(void) { return 108; }
 
 const char* fa8_error_string(int code) {
   switch (code) {
@@ -297,6 +325,37 @@ int fa8_quantize_e4m3_segments(const void* src, int32_t src_dtype, void* dst, in
   if ((reinterpret_cast<uintptr_t>(amax) & 3u) || (reinterpret_cast<uintptr_t>(descale) & 3u)) return FA8_ERR_BAD_ARG;
   cudaError_t e = fa8::launch_quantize(src, src_dtype == FA8_DTYPE_BF16, dst, seg_len, n_seg, amax, descale,
                                        static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) {
+    set_detail("quantize launch", cudaGetErrorString(e));
+    return FA8_ERR_CUDA;
+  }
+  return FA8_OK;
+}
+
+int fa8_quantize_e4m3_segments_noalloc(const void* src, int32_t src_dtype, void* dst, int64_t seg_len,
+                                       int32_t n_seg, float* descale, void* cuda_stream) {
+  g_detail[0] = '\0';
+  if (!src || !dst || !descale || seg_len <= 0 || n_seg <= 0) return FA8_ERR_BAD_ARG;
+  if (src_dtype != FA8_DTYPE_FP16 && src_dtype != FA8_DTYPE_BF16) return FA8_ERR_BAD_ARG;
+  if (!aligned16(src) || !aligned16(dst) || (n_seg > 1 && (seg_len % 8) != 0)) return FA8_ERR_BAD_ARG;
+  if (reinterpret_cast<uintptr_t>(descale) & 3u) return FA8_ERR_BAD_ARG;
+  if (n_seg > FA8_NOALLOC_MAX_SEGMENTS) {
+    char buf[128];
+    std::snprintf(buf, sizeof(buf), "%d segments asked for, the built-in scratch holds %d; use "
+                  "fa8_quantize_e4m3_segments with a buffer of your own", n_seg, FA8_NOALLOC_MAX_SEGMENTS);
+    set_detail("fa8_quantize_e4m3_segments_noalloc", buf);
+    return FA8_ERR_UNSUPPORTED;
+  }
+  cudaError_t e = cudaSuccess;
+  float* amax = quant_scratch(&e);
+  if (!amax) {
+    set_detail("cudaGetSymbolAddress (quantiser scratch)", cudaGetErrorString(e));
+    return FA8_ERR_CUDA;
+  }
+  // launch_quantize clears the n_seg maxima it is about to accumulate (stream-ordered), runs the
+  // two passes and allocates nothing.
+  e = fa8::launch_quantize(src, src_dtype == FA8_DTYPE_BF16, dst, seg_len, n_seg, amax, descale,
+                           static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess) {
     set_detail("quantize launch", cudaGetErrorString(e));
     return FA8_ERR_CUDA;

@@ -140,6 +140,28 @@ int fa8_quantize_e4m3(const void* src, int32_t src_dtype, void* dst, int64_t n, 
 int fa8_quantize_e4m3_segments(const void* src, int32_t src_dtype, void* dst, int64_t seg_len,
                                int32_t n_seg, float* amax, float* descale, void* cuda_stream);
 
+/* The same per-segment quantisation for callers that cannot allocate (it has no counterpart in the
+ * reference, whose callers cast with torch, test.py:20-22).  fa8_quantize_e4m3_segments wants
+ * a device buffer for the per-segment maxima even from a caller that only needs the descales.
+ * Code that runs where device memory must not be requested - a plug-in inside a framework that has
+ * frozen its memory plan, a callback on a serving path whose allocator is off limits, a region
+ * that is being captured into a graph, where cudaMalloc is an error - has no such buffer to give.
+ * Here the maxima live in a file-scope device array of the library: FA8_NOALLOC_MAX_SEGMENTS
+ * floats (16 KB), present on every GPU that loads the library until the process ends.  The call
+ * allocates nothing, neither with cudaMalloc nor through any library: it clears the n_seg entries it
+ * needs (stream-ordered) and enqueues the two passes on `cuda_stream`; src, dst and descale are the
+ * caller's, as before (descale must not be NULL: it is the only way the scales come out).
+ *   - n_seg above FA8_NOALLOC_MAX_SEGMENTS is refused with FA8_ERR_UNSUPPORTED (the detail
+ *     string names both numbers); seg_len a multiple of 8 unless n_seg is 1.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, once
+ *     per device, with that device current): make that first call outside any stream capture.
+ *   - Every call on a device uses the same array, which keeps the last call's maxima: two calls
+ *     that overlap on the GPU (different streams, no ordering between them) race on it.  Calls on
+ *     one stream, or ordered by events, are safe. */
+#define FA8_NOALLOC_MAX_SEGMENTS 4096
+int fa8_quantize_e4m3_segments_noalloc(const void* src, int32_t src_dtype, void* dst, int64_t seg_len,
+                                       int32_t n_seg, float* descale, void* cuda_stream);
+
 /* Failure-detection self-test (no counterpart in the reference, whose only error path is
  * exit(), include/attention_api.cuh:20-29): enqueues a one-warp kernel that waits on a barrier
  * nobody completes, using the same bounded wait as the attention kernel.  After `limit_us`
@@ -164,8 +186,8 @@ const char* fa8_last_error_detail(void);
 /* ABI version of this header: major*100 + minor (101 added softmax_lse, 102 heads_kv, 103 the
  * descale pointers and fa8_quantize_e4m3, 104 fp8_format, 105 seqlen_k, 106 descale_per_head and
  * fa8_quantize_e4m3_segments, 107 the library-owned status word and host-side failure flag,
- * sequence lengths free of the multiple-of-16 rule except for transposed V; new fields go at
- * the end of fa8_fwd_params). */
+ * sequence lengths free of the multiple-of-16 rule except for transposed V, 108
+ * fa8_quantize_e4m3_segments_noalloc; new fields go at the end of fa8_fwd_params). */
 int fa8_version(void);
 
 #ifdef __cplusplus

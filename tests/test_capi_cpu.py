@@ -18,7 +18,7 @@ def test_library_builds_and_loads():
     build()
     assert os.path.exists(LIB_PATH)
     lib = _lib.load()
-    assert lib.fa8_version() == 107
+    assert lib.fa8_version() == 108
 
 
 def test_every_declared_symbol_is_exported():
