@@ -6,44 +6,47 @@
 // csrc/mma_traits_sm89.hpp) and the C->A register shuffle (csrc/reg2reg.h).
 //
 // The grid is persistent (one CTA per SM); a CTA takes one work item after the other,
-// each being two 128-row query tiles of one (batch, head) slice, and walks the
-// key/value sequence; K and V^T arrive as 128-position tiles, the arithmetic runs
-// on 64-position sub-blocks so that each query tile has TWO score buffers in
-// tensor memory and its next S = Q K^T is computed while the softmax of the
-// current sub-block is still running:
+// each being two 128-row query tiles of one (batch, head) slice (one tile at head_dim
+// 256), and walks the key/value sequence; K and V^T arrive as 128-position tiles, the
+// arithmetic runs on 64-position sub-blocks so that each query tile has two (head_dim
+// 64: three) score buffers in tensor memory and its next S = Q K^T is computed while
+// the softmax of the current sub-block is still running:
 //
 //   warp 18     TMA producer: Q tiles (double-buffered across work items), then K_j /
 //               V_j tiles into a ring of shared-memory slots, each guarded by a
 //               full/empty mbarrier pair.
 //   warps 16,17 MMA issuers, one per query tile (one elected lane each):
-//               S_i[sb&1] = Q_i K_sb^T (M128 N64) and O_i += P_i(sb) V_sb
+//               S_i[sb % kSBuf] = Q_i K_sb^T (M128 N64) and O_i += P_i(sb) V_sb
 //               (M128 N=head_dim) as tcgen05.mma kind::f8f6f4 with fp32 accumulators
 //               in tensor memory; completion is signalled with tcgen05.commit on
 //               mbarriers.
 //   warps 0-7   online softmax for query tile 0, warps 8-15 for tile 1.  A TMEM lane
 //               is a query row (tcgen05.ld 32x32b: one row per thread, no shuffles).
-//               Warps w and w+4 of a tile own the same 32 rows: the first takes the
-//               even sub-blocks (S buffer 0), the second the odd ones (S buffer 1),
-//               so four softmax warps per scheduler keep the special-function and
-//               FMA pipes fed.  exp2 with the scale folded in, row sum from the fp32
+//               Warps w and w+4 of a tile own the same 32 rows and take the sub-blocks
+//               in turn, so four softmax warps per scheduler keep the special-function
+//               and FMA pipes fed.  exp2 with the scale folded in, row sum from the fp32
 //               probabilities, P re-quantised to e4m3 and written back to TMEM over
 //               its own S buffer as the A operand of the second GEMM; fp32 rescale of
-//               O in TMEM when the row maximum has to be raised.
+//               O in TMEM when the row maximum has to be raised.  At the end of a work
+//               item each warp scales its share of O, stages it as fp16 in shared
+//               memory and hands it to the copy engine as a tiled bulk store.
 //
-// TMEM columns: tile i has S buffers at 128*i and 128*i+64 (64 fp32 columns each;
-// P, 64 e4m3 = 16 columns, overlays the buffer it was computed from) and O_i at
-// 256 + head_dim*i.
+// TMEM columns: tile i owns [256*i, 256*i + 256) (all 512 at head_dim 256): its S buffers
+// at +64*b (64 fp32 columns each; P, 64 e4m3 = 16 columns, overlays the buffer it was
+// computed from), O_i after them (Cfg<D>).
 //
 // Numerics follow the reference: P = exp(scale*(S - m)) unnormalised, converted to
 // e4m3 round-to-nearest-even/saturating (csrc/flash_attention.cu:163-179,524), the
 // row sum taken from fp32 P (:239-240,:264-271), final O/l with the zero/NaN guard
 // (:542-554).  Differences: the output is fp16 (the reference rounds it to e4m3,
 // :556-557); m is the exact row maximum after the first sub-block and is then
-// raised only when a sub-block would push P beyond 2^8 (the reference raises it on
-// every block, :233-273), which leaves O/l unchanged up to the rounding of P.
+// raised only when a sub-block's sum of P would exceed 448, the largest e4m3 value (the
+// reference raises it on every block, :233-273), which leaves O/l unchanged up to the
+// rounding of P.
 //
 // Every mbarrier wait is bounded: when a wait runs out, the waiting thread
-// records a code in the caller's status word, raises a CTA-wide abort flag and
+// records a code in the status word and in the library's host-visible flag, raises a
+// CTA-wide abort flag and
 // every role leaves its loop, drains its own copies / MMAs (bounded again),
 // frees tensor memory and returns.
 #include <cuda.h>
@@ -1118,12 +1121,7 @@ static cudaError_t launch_one(const CUtensorMap& tq, const CUtensorMap& tk, cons
   }
   // Persistent grid: one CTA per SM (shared and tensor memory allow no more), each walking
   // its share of the work units.
-#ifdef FA8_ONE_UNIT_PER_CTA
-  dim3 grid(args.n_units, 1, 1);
-  (void)sms;
-#else
   dim3 grid(args.n_units < sms ? args.n_units : sms, 1, 1);
-#endif
   kernel<<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, args);
   return cudaGetLastError();
 }
@@ -1132,17 +1130,12 @@ template <int D, bool kCausal>
 static cudaError_t launch_layout(bool v_natural, bool e5m2, const CUtensorMap& tq, const CUtensorMap& tk,
                                  const CUtensorMap& tv, const CUtensorMap& to, const KernelArgs& args,
                                  cudaStream_t stream) {
-#ifdef FA8_SUBSET
-  if (v_natural || e5m2) return cudaErrorInvalidValue;
-  return launch_one<D, kCausal, false, false>(tq, tk, tv, to, args, stream);
-#else
   if (v_natural) {
     return e5m2 ? launch_one<D, kCausal, true, true>(tq, tk, tv, to, args, stream)
                 : launch_one<D, kCausal, true, false>(tq, tk, tv, to, args, stream);
   }
   return e5m2 ? launch_one<D, kCausal, false, true>(tq, tk, tv, to, args, stream)
               : launch_one<D, kCausal, false, false>(tq, tk, tv, to, args, stream);
-#endif
 }
 
 cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, const CUtensorMap& tq,
@@ -1156,12 +1149,10 @@ cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, con
     return causal ? launch_layout<64, true>(v_natural, e5m2, tq, tk, tv, to, args, stream)
                   : launch_layout<64, false>(v_natural, e5m2, tq, tk, tv, to, args, stream);
   }
-#ifndef FA8_SUBSET
   if (head_dim == 256) {
     return causal ? launch_layout<256, true>(v_natural, e5m2, tq, tk, tv, to, args, stream)
                   : launch_layout<256, false>(v_natural, e5m2, tq, tk, tv, to, args, stream);
   }
-#endif
   return cudaErrorInvalidValue;
 }
 
