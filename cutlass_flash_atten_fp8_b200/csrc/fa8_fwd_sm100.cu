@@ -137,8 +137,17 @@ struct Cfg {
   // from registers touches 32 different 128-byte lines per instruction; measured, that made the
   // write-out of a work item cost 2600 cycles).  The width is what the shared memory left beside
   // the ring allows: 2 KB per warp, 1 KB at head_dim 128.
-  static constexpr int kEpiCols = (D == 128) ? 16 : 32;
-  static constexpr int kEpiBytes = 32 * kEpiCols * 2;                  // per warp
+#ifndef FA8_EPI_COLS_128
+#define FA8_EPI_COLS_128 16
+#endif
+#ifndef FA8_EPI_BUFS_128
+#define FA8_EPI_BUFS_128 1
+#endif
+  static constexpr int kEpiCols = (D == 128) ? FA8_EPI_COLS_128 : epi_cols(D);
+  static_assert(kEpiCols == epi_cols(D), "the host builds O's tensor map from epi_cols()");
+  // Staging buffers per warp: with two, the copy engine reads one while the warp fills the other.
+  static constexpr int kEpiBufs = (D == 128) ? FA8_EPI_BUFS_128 : 1;
+  static constexpr int kEpiBytes = kEpiBufs * 32 * kEpiCols * 2;       // per warp
   static constexpr int kEpiWarps = 4 * kW * kTiles;                    // softmax warps that have rows
   static constexpr int kEpiOffset = kQBytes + kRingBytes;
   static constexpr int kBarOffset = kEpiOffset + kEpiWarps * kEpiBytes;
@@ -1027,10 +1036,15 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   #pragma unroll
           for (int q = 0; q < kMyCols / kEC; ++q) {
             uint32_t orow[kEC];
-            if constexpr (kEC == 16) tmem_ld_32x32b_x16(t_o + h * kMyCols + kEC * q, orow);
+            if constexpr (kEC == 8) tmem_ld_32x32b_x8(t_o + h * kMyCols + kEC * q, orow);
+            else if constexpr (kEC == 16) tmem_ld_32x32b_x16(t_o + h * kMyCols + kEC * q, orow);
             else tmem_ld_32x32b_x32(t_o + h * kMyCols + kEC * q, orow);
-            // the staging buffer is free once the copy engine has read the store before this one
-            if (lane == 0) bulk_wait_group_read0();
+            // a staging buffer is free once the copy engine has read the store that last used it
+            const uint32_t s_buf = s_stage + static_cast<uint32_t>((q % C::kEpiBufs) * 32 * kEC * 2);
+            if (lane == 0) {
+              if constexpr (C::kEpiBufs == 2) bulk_wait_group_read1();
+              else bulk_wait_group_read0();
+            }
             tmem_wait_ld();
             if (q == kMyCols / kEC - 1) {
               tc_fence_before();
@@ -1039,20 +1053,25 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             } else {
               __syncwarp();
             }
-  #pragma unroll
-            for (int e = 0; e < kEC; e += 8) {
-              st_shared_v4(s_stage + static_cast<uint32_t>(lane * kEC * 2 + e * 2),
-                           pack_half2(__uint_as_float(orow[e + 0]) * inv, __uint_as_float(orow[e + 1]) * inv),
-                           pack_half2(__uint_as_float(orow[e + 2]) * inv, __uint_as_float(orow[e + 3]) * inv),
-                           pack_half2(__uint_as_float(orow[e + 4]) * inv, __uint_as_float(orow[e + 5]) * inv),
-                           pack_half2(__uint_as_float(orow[e + 6]) * inv, __uint_as_float(orow[e + 7]) * inv));
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
+            // Chunks past head_dim (a padded head dim) or past the last query row are not staged
+            // at all: a skipped store commits no group, and the count of groups in flight is what
+            // tells when a staging buffer may be written again.
             const int col0 = h * kMyCols + kEC * q;
-            if (lane == 0 && col0 < d_out && row0_warp < seqlen) {
-              tma_store_3d(&tm_o, s_stage, col0, row0_warp, w.bh);
-              bulk_commit_group();
+            if (col0 < d_out && row0_warp < seqlen) {
+  #pragma unroll
+              for (int e = 0; e < kEC; e += 8) {
+                st_shared_v4(s_buf + static_cast<uint32_t>(lane * kEC * 2 + e * 2),
+                             pack_half2(__uint_as_float(orow[e + 0]) * inv, __uint_as_float(orow[e + 1]) * inv),
+                             pack_half2(__uint_as_float(orow[e + 2]) * inv, __uint_as_float(orow[e + 3]) * inv),
+                             pack_half2(__uint_as_float(orow[e + 4]) * inv, __uint_as_float(orow[e + 5]) * inv),
+                             pack_half2(__uint_as_float(orow[e + 6]) * inv, __uint_as_float(orow[e + 7]) * inv));
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&tm_o, s_buf, col0, row0_warp, w.bh);
+                bulk_commit_group();
+              }
             }
           }
           ++items;

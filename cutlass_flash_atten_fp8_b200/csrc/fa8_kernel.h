@@ -47,7 +47,10 @@ cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, con
                        cudaStream_t stream);
 
 // fp16 columns per store box of the kernel built for head dim 64, 128 or 256.
-constexpr int epi_cols(int kernel_head_dim) { return kernel_head_dim == 128 ? 16 : 32; }
+#ifndef FA8_EPI_COLS_128
+#define FA8_EPI_COLS_128 16
+#endif
+constexpr int epi_cols(int kernel_head_dim) { return kernel_head_dim == 128 ? FA8_EPI_COLS_128 : 32; }
 
 // One warp waits (bounded by limit_ns) on a barrier that never completes; see fa8_selftest_expired_wait.
 cudaError_t launch_expired_wait(int* status, int* host_status, unsigned long long limit_ns, cudaStream_t stream);
