@@ -184,7 +184,7 @@ class HostRunner:
     pinned if the download is to overlap).  Device buffers are allocated once per shape and
     reused.  Each runner has its own device status word."""
 
-    def __init__(self, device: Optional[torch.device] = None, chunks: int = 16, timing: bool = False):
+    def __init__(self, device: Optional[torch.device] = None, chunks: int = 8, timing: bool = False):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.chunks = max(1, int(chunks))
         # timing=True brackets every copy group and kernel with CUDA events and leaves the busy
