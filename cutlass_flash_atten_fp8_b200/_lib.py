@@ -26,7 +26,8 @@ FA8_DTYPE_BF16 = 1
 # Every symbol include/fa8_b200.h declares.
 EXPORTED_SYMBOLS = ("fa8_fwd", "fa8_check_status", "fa8_supported", "fa8_error_string",
                     "fa8_last_error_detail", "fa8_version", "fa8_selftest_expired_wait",
-                    "fa8_quantize_e4m3", "fa8_quantize_e4m3_segments", "fa8_quantize_e4m3_segments_noalloc")
+                    "fa8_quantize_e4m3", "fa8_quantize_e4m3_segments", "fa8_quantize_e4m3_segments_noalloc",
+                    "fa8_work_plan")
 FA8_NOALLOC_MAX_SEGMENTS = 4096
 
 
@@ -77,6 +78,8 @@ def load() -> ctypes.CDLL:
     lib.fa8_quantize_e4m3_segments_noalloc.restype = ctypes.c_int
     lib.fa8_supported.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.fa8_supported.restype = ctypes.c_int
+    lib.fa8_work_plan.argtypes = [ctypes.c_int32] * 6 + [ctypes.POINTER(ctypes.c_int32 * 4)]
+    lib.fa8_work_plan.restype = ctypes.c_int
     lib.fa8_error_string.argtypes = [ctypes.c_int]
     lib.fa8_error_string.restype = ctypes.c_char_p
     lib.fa8_last_error_detail.argtypes = []
@@ -85,6 +88,17 @@ def load() -> ctypes.CDLL:
     lib.fa8_version.restype = ctypes.c_int
     _lib = lib
     return lib
+
+
+def work_plan(slices: int, seqlen: int, head_dim: int, causal: bool, sm_count: int, seqlen_k: int = 0) -> dict:
+    """fa8_work_plan as a dict: how a launch of this shape is cut into work items on a GPU
+    with `sm_count` SMs (host arithmetic only)."""
+    lib = load()
+    out = (ctypes.c_int32 * 4)()
+    rc = lib.fa8_work_plan(slices, seqlen, seqlen_k, head_dim, int(causal), sm_count, ctypes.byref(out))
+    if rc != FA8_OK:
+        raise ValueError(error_message(rc))
+    return {"rows_per_item": out[0], "paired": bool(out[1]), "items_per_slice": out[2], "units": out[3]}
 
 
 def error_message(code: int) -> str:

@@ -184,7 +184,7 @@ int collect_earlier_failure(DeviceState* st, int32_t* caller_word, cudaStream_t 
 
 extern "C" {
 
-int fa8_version(void) { return 108; }
+int fa8_version(void) { return 109; }
 
 const char* fa8_error_string(int code) {
   switch (code) {
@@ -209,6 +209,26 @@ int fa8_supported(int32_t seqlen_k, int32_t head_dim, int32_t v_layout) {
   // the copy engine wants row strides in multiples of 16 bytes.  Rows of Q, K and natural V are
   // head_dim bytes, so their sequence lengths are free.
   if (v_layout == FA8_V_TRANSPOSED && (seqlen_k % 16) != 0) return FA8_ERR_UNSUPPORTED;
+  return FA8_OK;
+}
+
+// head dim of the kernel that serves `head_dim` (the next of 64, 128, 256)
+static int kernel_head_dim(int32_t head_dim) { return head_dim <= 64 ? 64 : (head_dim <= 128 ? 128 : 256); }
+
+int fa8_work_plan(int32_t slices, int32_t seqlen, int32_t seqlen_k, int32_t head_dim, int32_t is_causal,
+                  int32_t sm_count, int32_t plan[4]) {
+  if (!plan || slices <= 0 || seqlen <= 0 || seqlen_k < 0 || sm_count <= 0) return FA8_ERR_BAD_ARG;
+  if (head_dim < 32 || head_dim > 256 || (head_dim % 32) != 0) return FA8_ERR_UNSUPPORTED;
+  if (static_cast<int64_t>(slices) * ((static_cast<int64_t>(seqlen) + 127) / 128) > 0x7fffffff) return FA8_ERR_UNSUPPORTED;
+  fa8::KernelArgs a{};
+  a.n_slices = slices;
+  a.seqlen = seqlen;
+  a.seqlen_k = seqlen_k > 0 ? seqlen_k : seqlen;
+  if (!fa8::plan_fwd(kernel_head_dim(head_dim), is_causal != 0, a, sm_count)) return FA8_ERR_UNSUPPORTED;
+  plan[0] = a.rows_per_item;
+  plan[1] = a.fold;
+  plan[2] = a.n_pairs;
+  plan[3] = a.n_units;
   return FA8_OK;
 }
 
@@ -251,7 +271,7 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   // keep the true extent and the copy engine fills the box's missing columns (rows, for V^T)
   // with zeros, which add nothing to either product.  Rows longer than 128 bytes are copied as
   // column blocks of 128 bytes.
-  const uint32_t d_box = (p->head_dim <= 64) ? 64u : (p->head_dim <= 128 ? 128u : 256u);
+  const uint32_t d_box = static_cast<uint32_t>(kernel_head_dim(p->head_dim));
   const uint32_t d_blk = d_box < 128u ? d_box : 128u;
   const CUtensorMapSwizzle sw_qk = (d_box >= 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap tq, tk, tv, to;
@@ -285,12 +305,9 @@ int fa8_fwd(const fa8_fwd_params* p, void* cuda_stream) {
   args.heads_kv = heads_kv;
   args.softmax_scale = p->softmax_scale;
   args.timeout_ns = 2000000000ull;
-  // work items hold two 128-row query tiles, one at head_dim 256 (see the kernel's Cfg)
-  const int rows_per_item = (d_box == 256u) ? 128 : 256;
-  args.n_pairs = (p->seqlen + rows_per_item - 1) / rows_per_item;
-  const int64_t per_slice = p->is_causal ? (args.n_pairs + 1) / 2 : args.n_pairs;
-  if (bh * per_slice > 0x7fffffff) return FA8_ERR_UNSUPPORTED;
-  args.n_units = static_cast<int>(bh * per_slice);
+  // one work item per 128 query rows is the finest plan the launcher can choose
+  if (bh * ((static_cast<int64_t>(p->seqlen) + 127) / 128) > 0x7fffffff) return FA8_ERR_UNSUPPORTED;
+  args.n_slices = static_cast<int>(bh);
   cudaError_t e = fa8::launch_fwd(static_cast<int>(d_box), p->is_causal != 0, p->v_layout == FA8_V_NATURAL,
                                   p->fp8_format == FA8_FP8_E5M2, tq, tk, tv, to, args, stream);
   if (e != cudaSuccess) {

@@ -419,18 +419,21 @@ struct Item {
 };
 
 // Work decomposition of the persistent grid.  CTA c takes units c, c + gridDim.x, ...
-// Non-causal: a unit is one tile pair, slice-major (the CTAs running side by side work on
-// the same few slices, whose K and V stay in L2).  Causal: the cost of a pair grows with
-// its position, so a unit folds pair f with pair n-1-f of the same slice (heavy one
-// first) and every unit costs the same.
+// A work item is rows_per_item query rows of one slice: both tiles of the CTA, or (small
+// problems, see plan_work) one tile, the second staying idle.  Non-causal: a unit is one
+// item, slice-major (the CTAs running side by side work on the same few slices, whose K and
+// V stay in L2).  Causal: the cost of an item grows with its position, so a unit folds item
+// f with item n-1-f of the same slice (heavy one first) and every unit costs the same;
+// without folding (a grid with an SM for every item) a unit is one item, heaviest first.
 template <bool kCausal, int kTiles>
 __device__ __forceinline__ bool get_item(const KernelArgs& a, int unit, int k, Item& it) {
   const int n_pairs = a.n_pairs;
   int pair;
-  if (!kCausal) {
+  if (!kCausal || !a.fold) {
     if (k > 0) return false;
     it.bh = unit / n_pairs;
     pair = unit - it.bh * n_pairs;
+    if (kCausal) pair = n_pairs - 1 - pair;
   } else {
     const int n_fold = (n_pairs + 1) >> 1;
     it.bh = unit / n_fold;
@@ -443,12 +446,12 @@ __device__ __forceinline__ bool get_item(const KernelArgs& a, int unit, int k, I
       pair = f;
     }
   }
-  it.row0 = pair * kTiles * kTileM;
+  it.row0 = pair * a.rows_per_item;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int r0 = it.row0 + i * kTileM;
     int n = 0;
-    if (i < kTiles && r0 < a.seqlen) {
+    if (i < kTiles && i * kTileM < a.rows_per_item && r0 < a.seqlen) {
       // one past the last visible key; the causal mask is aligned top-left (key <= query row),
       // like the reference's (csrc/flash_attention.cu:24-71, test.py:25-33)
       const int col_end = kCausal ? min(r0 + kTileM, a.seqlen_k) : a.seqlen_k;
@@ -1112,6 +1115,62 @@ cudaError_t launch_expired_wait(int* status, int* host_status, unsigned long lon
 }
 
 // ------------------------------------------------------------------- launcher
+// Chooses the work items of one launch (rows_per_item, n_pairs, fold, n_units of KernelArgs).
+// Large problems: items of both query tiles, causal ones folded into equal-cost units - the
+// steady state of the kernel.  When that leaves more than half of the SMs without work, the
+// finer plans that still fit one wave of the grid are weighed by an estimate of the longest
+// unit in 64-key steps: an item costs its sub-blocks plus kBoundarySteps (pipeline ramp at each
+// item), and a step of a one-tile item costs kSingleStep of a two-tile one (eight softmax
+// warps instead of sixteen share the special-function unit).  Both constants are fits to
+// launches of 16-64 slices of 1024-4096 rows: a step 0.6 us, a boundary 3 us, one-tile steps
+// 0.41 us.  Plans of several waves of one-tile items were measured too and lose (the boundary
+// is paid per tile).  A tile's result does not depend on the plan: each tile is computed by
+// its own warps from its own tensor-memory columns in either.
+#ifndef FA8_PLAN
+#define FA8_PLAN 0          // 0 choose; 1-4 force candidate 0-3 (measurement builds)
+#endif
+template <int kTiles, bool kCausal>
+static void plan_work(KernelArgs& a, int sms) {
+  constexpr double kBoundarySteps = 5.0, kSingleStep = 0.68;
+  const int64_t slices = a.n_slices;
+  const int n_tiles = (a.seqlen + kTileM - 1) / kTileM;
+  struct Plan { int rows, fold; };
+  const Plan cand[4] = {{kTiles * kTileM, kCausal ? 1 : 0}, {kTileM, kCausal ? 1 : 0},
+                        {kTiles * kTileM, 0}, {kTileM, 0}};
+  auto items_of = [&](const Plan& p) { return (a.seqlen + p.rows - 1) / p.rows; };
+  auto units_of = [&](const Plan& p) {
+    const int n = items_of(p);
+    return slices * (p.fold ? (n + 1) / 2 : n);
+  };
+  auto steps_of = [&](const Plan& p) -> double {        // the longest unit, in two-tile steps
+    const int n = items_of(p);
+    auto item = [&](int idx) {
+      const int last_tile = min(idx * (p.rows / kTileM) + p.rows / kTileM - 1, n_tiles - 1);
+      const int col_end = kCausal ? min((last_tile + 1) * kTileM, a.seqlen_k) : a.seqlen_k;
+      return (col_end + kSubN - 1) / kSubN + kBoundarySteps;
+    };
+    const double unit = (p.fold && n > 1) ? item(n - 1) + item(0) : item(n - 1);
+    return unit * ((p.rows == kTileM && kTiles == 2) ? kSingleStep : 1.0);
+  };
+  int best = 0;
+  if (FA8_PLAN > 0) {
+    best = FA8_PLAN - 1;
+  } else if (2 * units_of(cand[0]) <= sms) {
+    double best_steps = steps_of(cand[0]);
+    for (int c = 1; c < 4; ++c) {
+      if (kTiles == 1 && cand[c].rows != cand[0].rows) continue;
+      if (!kCausal && c >= 2) continue;
+      if (units_of(cand[c]) > sms) continue;      // one wave (unfolded causal items differ in cost)
+      const double st = steps_of(cand[c]);
+      if (st < 0.95 * best_steps) { best = c; best_steps = st; }
+    }
+  }
+  a.rows_per_item = cand[best].rows;
+  a.fold = cand[best].fold;
+  a.n_pairs = items_of(cand[best]);
+  a.n_units = static_cast<int>(units_of(cand[best]));
+}
+
 template <int D>
 static constexpr int smem_bytes_for() { return Cfg<D>::kSmemBytes; }
 
@@ -1140,8 +1199,10 @@ static cudaError_t launch_one(const CUtensorMap& tq, const CUtensorMap& tk, cons
   }
   // Persistent grid: one CTA per SM (shared and tensor memory allow no more), each walking
   // its share of the work units.
-  dim3 grid(args.n_units < sms ? args.n_units : sms, 1, 1);
-  kernel<<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, args);
+  KernelArgs a = args;
+  plan_work<Cfg<D>::kTiles, kCausal>(a, sms);
+  dim3 grid(a.n_units < sms ? a.n_units : sms, 1, 1);
+  kernel<<<grid, kThreads, smem, stream>>>(tq, tk, tv, to, a);
   return cudaGetLastError();
 }
 
@@ -1156,6 +1217,19 @@ static cudaError_t launch_layout(bool v_natural, bool e5m2, const CUtensorMap& t
   return e5m2 ? launch_one<D, kCausal, false, true>(tq, tk, tv, to, args, stream)
               : launch_one<D, kCausal, false, false>(tq, tk, tv, to, args, stream);
 }
+
+bool plan_fwd(int head_dim, bool causal, KernelArgs& a, int sms) {
+  if (sms <= 0) return false;
+  if (head_dim == 256) {
+    causal ? plan_work<Cfg<256>::kTiles, true>(a, sms) : plan_work<Cfg<256>::kTiles, false>(a, sms);
+  } else if (head_dim == 64 || head_dim == 128) {
+    causal ? plan_work<2, true>(a, sms) : plan_work<2, false>(a, sms);
+  } else {
+    return false;
+  }
+  return true;
+}
+static_assert(Cfg<64>::kTiles == 2 && Cfg<128>::kTiles == 2, "plan_fwd assumes two query tiles per CTA at head dims 64 and 128");
 
 cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, const CUtensorMap& tq,
                        const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to, const KernelArgs& args,

@@ -19,8 +19,11 @@ struct KernelArgs {
   int head_dim;                   // row length of Q, K, V and O (<= the kernel's head dim)
   int heads;                      // query heads per batch entry
   int heads_kv;                   // K/V heads per batch entry (divides heads)
-  int n_pairs;                    // work items per slice: ceil(seqlen / 256), two 128-row query tiles each
-                                  // (ceil(seqlen / 128), one tile each, at head_dim 256)
+  int n_slices;                   // batch * heads
+  // Work plan, filled in by launch_fwd (see plan_work): the caller sets n_slices only.
+  int rows_per_item;              // query rows of a work item: 256 (two 128-row tiles) or 128 (one tile)
+  int n_pairs;                    // work items per slice: ceil(seqlen / rows_per_item)
+  int fold;                       // causal: a unit is item f followed by item n-1-f of a slice (equal cost)
   int n_units;                    // work units of the persistent grid (see get_item)
   float scale_log2;               // softmax_scale * log2(e)
   float o_scale;                  // multiplies O/l (1 = reference behaviour)
@@ -45,6 +48,11 @@ struct KernelArgs {
 cudaError_t launch_fwd(int head_dim, bool causal, bool v_natural, bool e5m2, const CUtensorMap& tq,
                        const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to, const KernelArgs& args,
                        cudaStream_t stream);
+
+// The work plan launch_fwd would choose on a GPU of `sms` SMs: fills rows_per_item, n_pairs,
+// fold and n_units of `a` from its seqlen, seqlen_k and n_slices.  Host arithmetic only.
+// head_dim is the kernel's (64, 128 or 256); false for any other or for sms <= 0.
+bool plan_fwd(int head_dim, bool causal, KernelArgs& a, int sms);
 
 // fp16 columns per store box of the kernel built for head dim 64, 128 or 256.
 #ifndef FA8_EPI_COLS_128

@@ -176,6 +176,19 @@ int fa8_selftest_expired_wait(int32_t* status_word, uint32_t limit_us, void* cud
  * reference (csrc/static_switch.h:50-77). */
 int fa8_supported(int32_t seqlen_k, int32_t head_dim, int32_t v_layout);
 
+/* How fa8_fwd would cut a problem of `slices` = batch * heads slices into work items on a GPU
+ * with `sm_count` SMs (host arithmetic; no GPU needed, nothing is launched).  Replaces the
+ * reference's grid calculation, (seqlen / 64, batch * heads) CTAs of one 64-row tile each
+ * (csrc/flash_attention.cu:586-610): here the grid is one CTA per SM and a CTA works through
+ * items of 256 query rows (two 128-row tiles side by side; one tile at head dims above 128);
+ * a causal unit pairs item f with item n-1-f of a slice so that all units cost the same.
+ * Problems that would leave more than half of the SMs idle are cut finer: items of 128 rows,
+ * or causal items as units of their own.  Results do not depend on the plan.
+ * plan[0] = query rows per item, plan[1] = 1 if causal items are paired, plan[2] = items per
+ * slice, plan[3] = units (the grid is min(units, sm_count) CTAs).  seqlen_k 0 = seqlen. */
+int fa8_work_plan(int32_t slices, int32_t seqlen, int32_t seqlen_k, int32_t head_dim, int32_t is_causal,
+                  int32_t sm_count, int32_t plan[4]);
+
 /* Static text for a return code.  Replaces the message printed by CUDA_ERROR_CHECK
  * (include/attention_api.cuh:20-29). */
 const char* fa8_error_string(int code);
@@ -187,7 +200,8 @@ const char* fa8_last_error_detail(void);
  * descale pointers and fa8_quantize_e4m3, 104 fp8_format, 105 seqlen_k, 106 descale_per_head and
  * fa8_quantize_e4m3_segments, 107 the library-owned status word and host-side failure flag,
  * sequence lengths free of the multiple-of-16 rule except for transposed V, 108
- * fa8_quantize_e4m3_segments_noalloc; new fields go at the end of fa8_fwd_params). */
+ * fa8_quantize_e4m3_segments_noalloc, 109 fa8_work_plan; new fields go at the end of
+ * fa8_fwd_params). */
 int fa8_version(void);
 
 #ifdef __cplusplus

@@ -14,7 +14,7 @@ import numpy as np
 import pytest
 import torch
 
-from cutlass_flash_atten_fp8_b200 import check_status, flash_attention_v2_cutlass, synth
+from cutlass_flash_atten_fp8_b200 import _lib, check_status, flash_attention_v2_cutlass, synth
 from oracle.attention_oracle import (attention_fp32, attention_fp32_rows, attention_quantised_p,
                                      error_metrics)
 
@@ -273,6 +273,35 @@ def test_bitwise_deterministic_and_reuses_out():
     b = run_kernel(q8, k8, v8, True, 0.09, out=buf)
     assert b.data_ptr() == buf.data_ptr()
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("D", [64, 128, 256])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("S", [192, 640, 1024, 1360])
+def test_work_plans_agree_bitwise(D, causal, S):
+    """A launch of a few slices is cut into finer work items than a launch that fills the GPU
+    (fa8_work_plan).  The same slices computed either way are bitwise identical, log-sum-exp
+    included, and the GPU-filling launch (the plan the full-size configurations run with) is
+    checked against the oracles on ragged and whole tile counts alike."""
+    sms = torch.cuda.get_device_properties(dev()).multi_processor_count
+    H, few = 80, 2
+    big_plan = _lib.work_plan(H, S, D, causal, sms)
+    small_plan = _lib.work_plan(few, S, D, causal, sms)
+    assert big_plan["rows_per_item"] == (128 if D > 128 else 256) and big_plan["paired"] == causal
+    if S > 128 and (D <= 128 or causal):      # one query tile per CTA above 128: only unpairing is finer
+        assert (small_plan["rows_per_item"], small_plan["paired"]) != (big_plan["rows_per_item"], big_plan["paired"])
+    q8, k8, v8 = (rand8(1, H, S, D, seed=300 + i) for i in range(3))
+    scale = 1.0 / math.sqrt(D)
+    d = dev()
+    qd, kd, vtd = q8.to(d), k8.to(d), v8.to(d).transpose(2, 3).contiguous()
+    o_big, lse_big = flash_attention_v2_cutlass(qd, kd, vtd, causal, scale, return_lse=True)
+    o_few, lse_few = flash_attention_v2_cutlass(qd[:, :few].contiguous(), kd[:, :few].contiguous(),
+                                                vtd[:, :few].contiguous(), causal, scale, return_lse=True)
+    check_status(d)
+    assert torch.equal(o_big[:, :few], o_few)
+    assert torch.equal(lse_big[:, :few], lse_few)
+    sel = [0, H - 1]
+    assert_close_to_oracles(o_big[:, sel], q8[:, sel], k8[:, sel], v8[:, sel], causal, scale)
 
 
 def test_operator_argument_errors_on_gpu():
