@@ -506,6 +506,8 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       reinterpret_cast<volatile uint32_t*>(smem_gen + C::kBarOffset + C::kNumBars * 8);
   volatile int* abort_flag =
       reinterpret_cast<volatile int*>(smem_gen + C::kBarOffset + C::kNumBars * 8 + 4);
+  volatile int* skip_flag =
+      reinterpret_cast<volatile int*>(smem_gen + C::kBarOffset + C::kNumBars * 8 + 8);
   RowGroupShared<C::kW>* groups =
       reinterpret_cast<RowGroupShared<C::kW>*>(smem_gen + C::kBarOffset + C::kNumBars * 8 + 16);
 
@@ -514,15 +516,10 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int seqlen = args.seqlen;
   const WaitCtx wctx{abort_flag, args.status, args.host_status, args.timeout_ns};
 
+  // Set-up, spread over three warps so that the three latencies overlap: thread 0 initialises
+  // the barriers, the first issuer warp allocates tensor memory, and lane 0 of warp 1 reads
+  // the status word from global memory.
   if (threadIdx.x == 0) {
-    // A status word that is already non-zero (an earlier CTA of this launch gave up, or the
-    // caller did not clear it) makes the CTA return at once: a failed launch then costs one
-    // wait limit, not one per CTA.
-    const bool stale = args.status != nullptr && *reinterpret_cast<volatile int*>(args.status) != 0;
-    *abort_flag = stale ? 2 : 0;
-    // The skipped launch leaves O unwritten: the host must hear of it even if the word's first
-    // report has already been collected.
-    if (stale && args.host_status != nullptr && *args.host_status == 0) *args.host_status = 0x5717;
     for (int x = 0; x < 4; ++x) {
       mbar_init(b_q_full + 8u * x, 1);
       mbar_init(b_q_empty + 8u * x, 1);
@@ -545,6 +542,21 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int g = 0; g < C::kGroups; ++g) groups[g].version = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
+  } else if (threadIdx.x == 32) {
+    // A status word that is already non-zero (an earlier CTA of this launch gave up, or the
+    // caller did not clear it) makes the CTA return at once: a failed launch then costs one
+    // wait limit, not one per CTA.  skip_flag is written here only; abort_flag is what a
+    // wait that gives up raises later.
+    const bool stale = args.status != nullptr && *reinterpret_cast<volatile int*>(args.status) != 0;
+    *abort_flag = stale ? 2 : 0;
+    *skip_flag = stale ? 1 : 0;
+    // The skipped launch leaves O unwritten: the host must hear of it even if the word's first
+    // report has already been collected.
+    if (stale && args.host_status != nullptr && *args.host_status == 0) *args.host_status = 0x5717;
+  } else if (warp == kLoadWarp && lane == 0) {
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
   }
   if (warp == kMmaWarp0) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_slot)), kTmemCols);
@@ -554,8 +566,7 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_slot;
-  const bool skip_cta = (*abort_flag == 2);
-  __syncthreads();            // nobody raises the flag before everyone has read it
+  const bool skip_cta = (*skip_flag != 0);
 
   // Warps 16-19 form a warpgroup of their own (producer, two MMA issuers, one spare): it
   // hands most of its registers to the four softmax warpgroups.
@@ -566,9 +577,6 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     } else if (warp == kLoadWarp) {
       // ------------------------------------------------------------ TMA producer
       if (elect_one()) {
-        prefetch_tensormap(&tm_q);
-        prefetch_tensormap(&tm_k);
-        prefetch_tensormap(&tm_v);
         bool ok = true;
         int it = 0;                 // K/V loads issued so far; slot = it % kSlots
         int qn[2] = {0, 0};         // Q loads issued so far per tile; stage = qn & 1
@@ -1080,7 +1088,9 @@ fa8_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           ++items;
         }
       }
-      if (lane == 0) bulk_wait_group0();      // this warp's stores of O have left shared memory and are complete
+      // This warp's stores of O have been read out of shared memory (the CTA may give it back);
+      // their writes to global memory are complete when the kernel is.
+      if (lane == 0) bulk_wait_group_read0();
     }
   }
 
