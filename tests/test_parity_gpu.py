@@ -304,6 +304,35 @@ def test_work_plans_agree_bitwise(D, causal, S):
     assert_close_to_oracles(o_big[:, sel], q8[:, sel], k8[:, sel], v8[:, sel], causal, scale)
 
 
+def test_same_addresses_with_other_shapes_and_other_addresses_with_the_same_shape():
+    """The library keeps the tensor maps of a thread's previous call and reuses them when
+    addresses, extents and layout all match: calls that differ in any one of them must not
+    see the earlier maps."""
+    d = dev()
+    q8, k8, v8 = (rand8(1, 4, 512, 64, seed=400 + i).to(d) for i in range(3))
+    scale = 0.125
+
+    def both(q, k, v, causal):
+        vt = v.transpose(2, 3).contiguous()
+        a = flash_attention_v2_cutlass(q, k, vt, causal, scale)[0]
+        b = flash_attention_v2_cutlass(q, k, vt, causal, scale)[0]      # same addresses except O
+        buf = torch.empty_like(a)
+        c = flash_attention_v2_cutlass(q, k, vt, causal, scale, out=buf)[0]
+        e = flash_attention_v2_cutlass(q, k, vt, causal, scale, out=buf)[0]   # every address the same
+        check_status(d)
+        assert torch.equal(a, b) and torch.equal(a, c) and torch.equal(a, e)
+        assert_close_to_oracles(a, q, k, v, causal, scale)
+
+    both(q8, k8, v8, False)
+    both(q8, k8, v8, True)
+    # the same storage read as eight slices of 256 rows: same addresses, other extents
+    both(q8.view(1, 8, 256, 64), k8.view(1, 8, 256, 64), v8.view(1, 8, 256, 64), False)
+    # same shape as the first call, other addresses
+    q2, k2, v2 = (rand8(1, 4, 512, 64, seed=410 + i).to(d) for i in range(3))
+    both(q2, k2, v2, False)
+    both(q8, k8, v8, False)
+
+
 def test_operator_argument_errors_on_gpu():
     d = dev()
     q = torch.zeros(1, 1, 128, 64, device=d).to(F8)
