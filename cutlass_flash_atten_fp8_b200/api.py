@@ -178,15 +178,18 @@ class HostRunner:
     device -> host copy of O.  The (batch, head) slices are independent, so the call is cut
     into `chunks` groups of slices and pipelined over three streams: the upload of group
     g+1, the kernel of group g and the download of group g-1 overlap, which uses both
-    directions of the host link at once.  The call returns after O has landed in pinned host
+    directions of the host link at once.  The last group is cut `taper` more times, each piece
+    half the one before: the kernel and the download of the final piece are all the call adds
+    to the time of the uploads.  The call returns after O has landed in pinned host
     memory: a tensor of its own for every call (torch's pinned-memory cache makes that cheap
     once an earlier result has been released), or the caller's `out=` (fp16, shaped like q;
     pinned if the download is to overlap).  Device buffers are allocated once per shape and
     reused.  Each runner has its own device status word."""
 
-    def __init__(self, device: Optional[torch.device] = None, chunks: int = 8, timing: bool = False):
+    def __init__(self, device: Optional[torch.device] = None, chunks: int = 8, timing: bool = False, taper: int = 3):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.chunks = max(1, int(chunks))
+        self.taper = max(0, int(taper))
         # timing=True brackets every copy group and kernel with CUDA events and leaves the busy
         # time of each stage of the last call in `last_timing` (milliseconds, summed over groups)
         self.timing = bool(timing)
@@ -210,9 +213,23 @@ class HostRunner:
         self._key = key
 
     @staticmethod
-    def _groups(n: int, parts: int):
+    def _groups(n: int, parts: int, taper: int = 0):
+        """[lo, hi) ranges of n slices: `parts` equal groups, the last of which is cut again
+        into `taper` + 1 pieces, each half the one before (the last two equal).  The upload
+        stream is busy from start to end; what the call adds to it is the kernel and the
+        download of the LAST group, so that one is made small."""
         parts = min(parts, n)
-        return [(n * g // parts, n * (g + 1) // parts) for g in range(parts)]
+        cuts = [n * g // parts for g in range(parts + 1)]
+        lo, hi = cuts[-2], cuts[-1]
+        tail = []
+        for _ in range(taper):
+            mid = lo + (hi - lo + 1) // 2
+            if mid >= hi:
+                break
+            tail.append(mid)
+            lo = mid
+        cuts = cuts[:-1] + tail + [hi]
+        return [(a, b) for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
 
     def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = False,
                  softmax_scale: float = 1.0, **kw) -> List[torch.Tensor]:
@@ -237,7 +254,7 @@ class HostRunner:
         if kw.get("return_lse") or per_head:
             groups = [(0, B * H if flat else B)]
         else:
-            groups = self._groups(B * H if flat else B, self.chunks)
+            groups = self._groups(B * H if flat else B, self.chunks, self.taper)
         if flat:
             hq, hk, hv, dq, dk, dv, do, ho = (t.view(1, B * t.shape[1], t.shape[2], t.shape[3])
                                               for t in (q, k, v, self.dq, self.dk, self.dv, self.do, host_out))
