@@ -178,18 +178,18 @@ class HostRunner:
     device -> host copy of O.  The (batch, head) slices are independent, so the call is cut
     into `chunks` groups of slices and pipelined over three streams: the upload of group
     g+1, the kernel of group g and the download of group g-1 overlap, which uses both
-    directions of the host link at once.  The last group is cut `taper` more times, each piece
-    half the one before: the kernel and the download of the final piece are all the call adds
-    to the time of the uploads.  The call returns after O has landed in pinned host
+    directions of the host link at once.  The last two groups are cut again into pieces that
+    shrink by the factor `taper` (see _groups), so that little is left to compute and download
+    when the last upload lands.  The call returns after O has landed in pinned host
     memory: a tensor of its own for every call (torch's pinned-memory cache makes that cheap
     once an earlier result has been released), or the caller's `out=` (fp16, shaped like q;
     pinned if the download is to overlap).  Device buffers are allocated once per shape and
     reused.  Each runner has its own device status word."""
 
-    def __init__(self, device: Optional[torch.device] = None, chunks: int = 8, timing: bool = False, taper: int = 3):
+    def __init__(self, device: Optional[torch.device] = None, chunks: int = 6, timing: bool = False, taper: float = 2.0 / 3.0):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.chunks = max(1, int(chunks))
-        self.taper = max(0, int(taper))
+        self.taper = min(max(0.0, float(taper)), 0.9)
         # timing=True brackets every copy group and kernel with CUDA events and leaves the busy
         # time of each stage of the last call in `last_timing` (milliseconds, summed over groups)
         self.timing = bool(timing)
@@ -213,23 +213,25 @@ class HostRunner:
         self._key = key
 
     @staticmethod
-    def _groups(n: int, parts: int, taper: int = 0):
-        """[lo, hi) ranges of n slices: `parts` equal groups, the last of which is cut again
-        into `taper` + 1 pieces, each half the one before (the last two equal).  The upload
-        stream is busy from start to end; what the call adds to it is the kernel and the
-        download of the LAST group, so that one is made small."""
+    def _groups(n: int, parts: int, taper: float = 0.0):
+        """[lo, hi) ranges of n slices: `parts` equal groups; with taper > 0 the last two of
+        them are cut again into pieces that shrink by that factor (each piece is 1 - taper of
+        what is left, at least two slices).  The upload stream is busy from start to end; what
+        the call adds to it is the kernel and the download of whatever has not been downloaded
+        when the last upload lands.  A download takes about two thirds of the time of the same
+        slices' upload, so pieces shrinking by two thirds keep the download stream from
+        falling behind while they get small."""
         parts = min(parts, n)
         cuts = [n * g // parts for g in range(parts + 1)]
-        lo, hi = cuts[-2], cuts[-1]
+        if taper <= 0.0 or parts < 2:
+            return [(a, b) for a, b in zip(cuts[:-1], cuts[1:])]
+        head, lo, hi = cuts[:-2], cuts[-3], cuts[-1]
         tail = []
-        for _ in range(taper):
-            mid = lo + (hi - lo + 1) // 2
-            if mid >= hi:
-                break
-            tail.append(mid)
-            lo = mid
-        cuts = cuts[:-1] + tail + [hi]
-        return [(a, b) for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
+        while lo < hi:
+            tail.append(lo)
+            lo += min(hi - lo, max(2, round((hi - lo) * (1.0 - taper))))
+        cuts = head[:-1] + tail + [hi]
+        return [(a, b) for a, b in zip(cuts[:-1], cuts[1:])]
 
     def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = False,
                  softmax_scale: float = 1.0, **kw) -> List[torch.Tensor]:
