@@ -469,6 +469,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--e2e-groups", type=int, default=None, help="slice groups of the end-to-end pipeline (default: HostRunner's)")
+    ap.add_argument("--e2e-taper", type=float, default=None, help="shrink factor of the tail groups (default: HostRunner's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", action="store_true",
                     help="kept for old command lines: the gather of O is always timed when N > 1 (gather_o_ms)")
@@ -583,7 +585,8 @@ def main():
     # ---- end to end: host tensors in, host tensor out, copies inside the timed region
     # Every step uploads the step's Q, K, V from pinned host memory and downloads O into a
     # pinned host tensor (the caller's `out=`, so that no allocation sits in the timed region).
-    runner = HostRunner(device)
+    runner_kw = {k: v for k, v in (("chunks", args.e2e_groups), ("taper", args.e2e_taper)) if v is not None}
+    runner = HostRunner(device, **runner_kw)
     hq, hk, hv = (torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in (q4, k4, v4))
     ho = torch.empty(out.shape, dtype=torch.float16, pin_memory=True)
     for _ in range(2):
